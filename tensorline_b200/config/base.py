@@ -85,7 +85,10 @@ def read_config_json(folder) -> dict:
 
 
 def architecture_name(raw: dict) -> str:
+    """`architectures[0]`, or the single name under `architecture`."""
     arch = raw.get("architectures")
+    if arch is None and isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
     if not (isinstance(arch, list) and arch and isinstance(arch[0], str)):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     return arch[0]

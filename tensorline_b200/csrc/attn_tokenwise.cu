@@ -5,6 +5,8 @@
 // A query at position p of a request reads the keys at positions lo..p of that request from the
 // cache pages, lo = 0 or p - window + 1 (tensorline/paged.py:237; tensorline/paged_attn.py:43).
 // s = (q . k) * scale, softmax over keys in float, o = P V (tensorline/paged_attn.py:46-57).
+// `sink` (float per query head, may be null): the denominator also holds exp(sink[h]), a term with no
+// key and no value that is not scaled and counts once.
 //
 // Keys are taken in tiles of 32 aligned to absolute position 0, each lane owning one key of the
 // tile, with a running maximum and sum.  The order of every addition depends only on the
@@ -19,7 +21,8 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
                                       const TA* __restrict__ k_pages, const TA* __restrict__ v_pages,
                                       const int* __restrict__ table, int max_pages, int page_size,
                                       const int* __restrict__ pos, const int* __restrict__ req_slot,
-                                      int nq, int nkv, int d, int window, float scale, const TlLimits L) {
+                                      int nq, int nkv, int d, int window, float scale,
+                                      const float* __restrict__ sink, const TlLimits L) {
     __shared__ float qs[ATT_MAX_D];
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int kh = h / (nq / nkv);
@@ -70,6 +73,13 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
         }
         m = m_new;
     }
+    if (sink) {                                          // one more term of the denominator: no key, no value
+        const float m_new = fmaxf(m, sink[h]);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sink[h] - m_new);
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) acc[c] *= alpha;
+    }
     TA* orow = out + ((size_t)t * nq + h) * d;
     const float inv = 1.0f / l;
 #pragma unroll
@@ -82,8 +92,8 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
 TL_EXPORT int tl_attn_tokenwise(const void* q, int q_stride, void* out, int act_dtype,
                                 const void* k_pages, const void* v_pages, const int* table, int max_pages,
                                 int page_size, const int* pos, const int* req_slot, int T, int nq, int nkv,
-                                int d, int window, float scale, int table_rows, int total_pages, int* fault,
-                                cudaStream_t stream) {
+                                int d, int window, float scale, const float* sink, int table_rows, int total_pages,
+                                int* fault, cudaStream_t stream) {
     const TlLimits L{table_rows, total_pages, fault};
     if (T <= 0) return 0;
     if (d > ATT_MAX_D || nq % nkv) return 1;
@@ -91,10 +101,10 @@ TL_EXPORT int tl_attn_tokenwise(const void* q, int q_stride, void* out, int act_
     if (act_dtype == TL_F32)
         attn_tokenwise_kernel<float><<<grid, 32, 0, stream>>>((const float*)q, q_stride, (float*)out,
             (const float*)k_pages, (const float*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale, L);
+            nq, nkv, d, window, scale, sink, L);
     else
         attn_tokenwise_kernel<bf16><<<grid, 32, 0, stream>>>((const bf16*)q, q_stride, (bf16*)out,
             (const bf16*)k_pages, (const bf16*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale, L);
+            nq, nkv, d, window, scale, sink, L);
     return tl_launch_status();
 }

@@ -2,8 +2,9 @@
 //
 // Each kernel has a plain reference in tests/plain/qwen2_plain.py.  Formulas:
 //   embedding   x[t,:] = E[ids[t],:]                       (tensorline/paged.py:240)
-//   add+RMSNorm x += r;  h = cast(x * rsqrt(mean(x^2)+eps)) * w   (tensorline/fused.py:19-32;
-//               the cast to the activation type comes before the weight multiply, fused.py:32)
+//   add+RMSNorm x += alpha r;  h = cast(x * rsqrt(mean(x^2)+eps)) * w   (tensorline/fused.py:19-32;
+//               the cast to the activation type comes before the weight multiply, fused.py:32; with
+//               `cast_first` 0 the norm is float to the end and only h is rounded; alpha = 1 is the plain sum)
 //   SwiGLU      m = silu(g) * u,  silu(z) = z / (1 + e^-z), from the fused gate|up product
 // The residual stream x is float in both engines, so the residual sum is a 32-bit sum.
 #include "common.cuh"
@@ -39,7 +40,8 @@ TL_EXPORT int tl_embed(void* x, const void* table, int table_dtype, const int* i
 template <typename TA, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ r,
                                    const TW* __restrict__ w, TA* __restrict__ out,
-                                   const int* __restrict__ rows, int H, float eps, int write_x) {
+                                   const int* __restrict__ rows, int H, float eps, int write_x, float alpha,
+                                   int cast_first) {
     __shared__ float red[33];
     const int i = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[i] : i) * H;
@@ -50,7 +52,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = xr[c];
         if (rr) {
-            v = v + to_f<TA>(rr[c]);
+            v = fmaf(alpha, to_f<TA>(rr[c]), v);
             if (write_x) xr[c] = v;
         }
         ss = fmaf(v, v, ss);
@@ -59,8 +61,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = xr[c];
-        if (rr && !write_x) v = v + to_f<TA>(rr[c]);
-        const float n = to_f<TA>(from_f<TA>(v * rstd));          // cast first, then the weight
+        if (rr && !write_x) v = fmaf(alpha, to_f<TA>(rr[c]), v);
+        const float n = cast_first ? to_f<TA>(from_f<TA>(v * rstd)) : v * rstd;      // cast first, then the weight
         o[c] = from_f<TA>(n * to_f<TW>(w[c]));
     }
 }
@@ -98,7 +100,8 @@ template <typename TA, typename TW, int NV, bool PIECES>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ r,
                                        const TW* __restrict__ w, TA* __restrict__ out,
                                        const int* __restrict__ rows, int H, float eps, int write_x,
-                                       const float* __restrict__ partial, int splits, size_t plane) {
+                                       const float* __restrict__ partial, int splits, size_t plane, float alpha,
+                                       int cast_first) {
     __shared__ float red[33];
     const int i = blockIdx.x, nvec = H >> 2;
     float v[NV][4], wv[NV][4];
@@ -137,7 +140,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                     for (int e = 0; e < 4; ++e) acc[e] += pv[e];
                 }
 #pragma unroll
-                for (int e = 0; e < 4; ++e) v[k][e] = v[k][e] + to_f<TA>(from_f<TA>(acc[e]));
+                for (int e = 0; e < 4; ++e) v[k][e] = fmaf(alpha, to_f<TA>(from_f<TA>(acc[e])), v[k][e]);
                 if (write_x) Vec4<float>::store(x + src + 4 * c, v[k]);
             }
         }
@@ -149,7 +152,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                 float rv[4];
                 Vec4<TA>::load(r + src + 4 * c, rv);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) v[k][e] = v[k][e] + rv[e];
+                for (int e = 0; e < 4; ++e) v[k][e] = fmaf(alpha, rv[e], v[k][e]);
                 if (write_x) Vec4<float>::store(x + src + 4 * c, v[k]);
             }
         }
@@ -168,7 +171,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
         if (c < nvec) {
             float o[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] = to_f<TA>(from_f<TA>(v[k][e] * rstd)) * wv[k][e];
+            for (int e = 0; e < 4; ++e) o[e] = (cast_first ? to_f<TA>(from_f<TA>(v[k][e] * rstd)) : v[k][e] * rstd) * wv[k][e];
             Vec4<TA>::store(out + (size_t)i * H + 4 * c, o);
         }
     }
@@ -176,15 +179,16 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
 
 template <typename TA, typename TW>
 static int launch_add_rmsnorm(void* x, const void* r, const void* w, void* out, const int* rows, int R, int H,
-                              float eps, int write_x, const float* partial, int splits, size_t plane, cudaStream_t stream) {
+                              float eps, int write_x, const float* partial, int splits, size_t plane, float alpha,
+                              int cast_first, cudaStream_t stream) {
     const int nvec = H >> 2;
     const bool vec = (H & 3) == 0 && nvec <= 8192 &&
                      ((((uintptr_t)x | (uintptr_t)r | (uintptr_t)w | (uintptr_t)out | (uintptr_t)partial) & 15) == 0);
     if (partial && !vec) return 1;                       // pieces only on the vector path; the caller sums them first
 #define VLAUNCH(NV) { int th = ((nvec + NV - 1) / NV + 31) / 32 * 32; \
-        if (partial) launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV, true>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane); \
-        else launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV, false>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane); }
-    if (!vec) add_rmsnorm_kernel<TA, TW><<<R, 256, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x);
+        if (partial) launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV, true>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane, alpha, cast_first); \
+        else launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV, false>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane, alpha, cast_first); }
+    if (!vec) add_rmsnorm_kernel<TA, TW><<<R, 256, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, alpha, cast_first);
     else if (nvec <= 1024) VLAUNCH(1)
     else if (nvec <= 2048) VLAUNCH(2)
     else if (nvec <= 4096) VLAUNCH(4)
@@ -195,15 +199,15 @@ static int launch_add_rmsnorm(void* x, const void* r, const void* w, void* out, 
 
 TL_EXPORT int tl_add_rmsnorm(void* x, const void* r, const void* w, int w_dtype, void* out, int act_dtype,
                              const int* rows, int R, int H, float eps, int write_x, const float* partial, int splits,
-                             long long plane, cudaStream_t stream) {
+                             long long plane, float alpha, int cast_first, cudaStream_t stream) {
     if (R <= 0) return 0;
     int e;
     if (act_dtype == TL_F32) {
-        if (w_dtype == TL_F32) e = launch_add_rmsnorm<float, float>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
-        else e = launch_add_rmsnorm<float, bf16>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
+        if (w_dtype == TL_F32) e = launch_add_rmsnorm<float, float>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, alpha, cast_first, stream);
+        else e = launch_add_rmsnorm<float, bf16>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, alpha, cast_first, stream);
     } else {
-        if (w_dtype == TL_F32) e = launch_add_rmsnorm<bf16, float>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
-        else e = launch_add_rmsnorm<bf16, bf16>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
+        if (w_dtype == TL_F32) e = launch_add_rmsnorm<bf16, float>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, alpha, cast_first, stream);
+        else e = launch_add_rmsnorm<bf16, bf16>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, alpha, cast_first, stream);
     }
     return e ? e : tl_launch_status();
 }

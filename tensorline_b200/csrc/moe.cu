@@ -1,0 +1,277 @@
+// Routed feed-forward (mixture of experts): router, choice of experts, and the experts' two products.
+//
+//   z = h Wr^T + br                         float, whatever the engine's activation type (small_proj)
+//   chosen = the `top` largest z, lowest index first on a tie; weights = softmax over the chosen z only
+//   y = sum_j weight_j * Wdown[e_j] act(Wup[e_j] h),   act(u) = relu(u)^2
+//
+// Two routes for the experts' products.  Steps of few tokens (decoding): every (token, chosen expert) pair streams its
+// expert's rows (moe_up), and every token sums its experts' down products in the order they were chosen (moe_down):
+// one pass over the weights the step needs, no sorting, nothing on the host, so the step can sit in a CUDA graph.
+// Steps of many tokens: the pairs are sorted by expert on the device (moe_sort), the tokens' rows gathered in that
+// order, every expert runs two dense products on its run of rows, and moe_combine sums each token's rows by weight.
+// Every output element is one fixed chain of additions, so a token's result does not depend on the step's other tokens.
+#include "common.cuh"
+
+// dot product of a weight row with a float vector in shared memory, lanes striding; every lane gets the sum
+template <typename TW> __device__ __forceinline__ float warp_dot(const TW* __restrict__ w, const float* __restrict__ x, int K, int lane);
+template <> __device__ __forceinline__ float warp_dot<float>(const float* __restrict__ w, const float* __restrict__ x, int K, int lane) {
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(w[k], x[k], acc);
+    return warp_sum(acc);
+}
+template <> __device__ __forceinline__ float warp_dot<bf16>(const bf16* __restrict__ w, const float* __restrict__ x, int K, int lane) {
+    float acc = 0.f;
+    if ((K & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+        for (int k = lane * 8; k < K; k += 256) {
+            const uint4 v = *reinterpret_cast<const uint4*>(w + k);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc = fmaf(__low2float(p[e]), x[k + 2 * e], acc);
+                acc = fmaf(__high2float(p[e]), x[k + 2 * e + 1], acc);
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(__bfloat162float(w[k]), x[k], acc);
+    }
+    return warp_sum(acc);
+}
+
+// ------------------------------------------------------------------ small projection in float
+// out[t, n] = bias[n] + sum_k h[t, k] w[n, k]: for outputs that must be 32-bit whatever the engine (router logits,
+// gate pre-activations of a recurrence).  One block per token; the token's row sits in shared memory as float.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128) small_proj_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ w,
+                                                         const TW* __restrict__ bias, float* __restrict__ out, int ldo, int N, int K) {
+    extern __shared__ float xs[];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * ldh + k]);
+    __syncthreads();
+    for (int n = wid; n < N; n += 4) {
+        const float v = warp_dot<TW>(w + (size_t)n * K, xs, K, lane);
+        if (lane == 0) out[(size_t)t * ldo + n] = v + (bias ? to_f<TW>(bias[n]) : 0.f);
+    }
+}
+
+TL_EXPORT int tl_small_proj(const void* h, int act_dtype, int ldh, const void* w, const void* bias, int w_dtype, float* out,
+                            int ldo, int T, int N, int K, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    const size_t smem = (size_t)K * sizeof(float);
+    if (smem > 48 * 1024) return 1;
+#define SP(TA, TW) small_proj_kernel<TA, TW><<<T, 128, smem, stream>>>((const TA*)h, ldh, (const TW*)w, (const TW*)bias, out, ldo, N, K)
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) SP(float, float); else SP(float, bf16); }
+    else { if (w_dtype == TL_F32) SP(bf16, float); else SP(bf16, bf16); }
+#undef SP
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ choice of experts
+// One warp per token.  `top` rounds of a warp-wide arg-max (largest value, lowest index on a tie); the weights are
+// the softmax over the chosen logits.  E <= 1024, top <= 32.
+__global__ void __launch_bounds__(128) topk_softmax_kernel(const float* __restrict__ z, int E, int top, int* __restrict__ idx,
+                                                           float* __restrict__ wts, int T) {
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* row = z + (size_t)t * E;
+    unsigned taken = 0;                                  // bit c: my element lane + 32 c is chosen
+    float mine = 0.f, first = 0.f, sum = 0.f;            // lane j keeps the j-th chosen logit
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY; int bi = 0x7fffffff;
+        for (int c = 0, e = lane; e < E; ++c, e += 32) {
+            const float v = row[e];
+            if (!((taken >> c) & 1u) && (v > best || (v == best && e < bi) || bi == 0x7fffffff)) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        if (j == 0) first = best;
+        const float p = expf(best - first);
+        sum += p;
+        if (lane == j) mine = p;
+        if (lane == 0) idx[(size_t)t * top + j] = bi;
+    }
+    if (lane < top) wts[(size_t)t * top + lane] = mine / sum;
+}
+
+TL_EXPORT int tl_topk_softmax(const float* z, int E, int top, int* idx, float* wts, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E > 1024 || top > 32 || top > E || top < 1) return 1;
+    topk_softmax_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, E, top, idx, wts, T);
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ experts, few tokens
+constexpr int MOE_ROWS = 32;                             // output rows a block (8 a warp)
+
+// a[pair, f] = relu(Wup[e][f, :] . h[t, :])^2, pair = t * top + j, e = idx[pair]
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, const TW* __restrict__ w_up, const int* __restrict__ idx,
+                                                     TA* __restrict__ a, int K, int F, int top) {
+    extern __shared__ float xs[];
+    const int pair = blockIdx.x, t = pair / top, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int e = idx[pair];
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * K + k]);
+    __syncthreads();
+    const TW* w = w_up + (size_t)e * F * K;
+    const int f0 = blockIdx.y * MOE_ROWS;
+    for (int f = f0 + wid; f < min(F, f0 + MOE_ROWS); f += 4) {
+        const float u = fmaxf(warp_dot<TW>(w + (size_t)f * K, xs, K, lane), 0.f);
+        if (lane == 0) a[(size_t)pair * F + f] = from_f<TA>(u * u);
+    }
+}
+
+// y[t, n] = sum_j wts[t, j] * (Wdown[e_j][n, :] . a[t * top + j, :]), j in the order chosen
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a, const TW* __restrict__ w_down, const int* __restrict__ idx,
+                                                       const float* __restrict__ wts, TA* __restrict__ y, int F, int N, int top) {
+    extern __shared__ float xs[];                        // [top][F]
+    const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < top * F; k += blockDim.x) xs[k] = to_f<TA>(a[(size_t)t * top * F + k]);
+    __syncthreads();
+    const int n0 = blockIdx.y * MOE_ROWS;
+    for (int n = n0 + wid; n < min(N, n0 + MOE_ROWS); n += 4) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int e = idx[(size_t)t * top + j];
+            const float v = warp_dot<TW>(w_down + ((size_t)e * N + n) * F, xs + (size_t)j * F, F, lane);
+            acc = fmaf(wts[(size_t)t * top + j], v, acc);
+        }
+        if (lane == 0) y[(size_t)t * N + n] = from_f<TA>(acc);
+    }
+}
+
+TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dtype, const int* idx, void* a, int P, int K,
+                        int F, int top, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    const size_t smem = (size_t)K * sizeof(float);
+    if (smem > 48 * 1024) return 1;
+    const dim3 grid(P, (F + MOE_ROWS - 1) / MOE_ROWS);
+    if (grid.y > 65535) return 1;
+#define MU(TA, TW) moe_up_kernel<TA, TW><<<grid, 128, smem, stream>>>((const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top)
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MU(float, float); else MU(float, bf16); }
+    else { if (w_dtype == TL_F32) MU(bf16, float); else MU(bf16, bf16); }
+#undef MU
+    return tl_launch_status();
+}
+
+TL_EXPORT int tl_moe_down(const void* a, int act_dtype, const void* w_down, int w_dtype, const int* idx, const float* wts,
+                          void* y, int T, int F, int N, int top, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t smem = (size_t)top * F * sizeof(float);
+    if (smem > 48 * 1024) return 1;
+    const dim3 grid(T, (N + MOE_ROWS - 1) / MOE_ROWS);
+    if (grid.y > 65535) return 1;
+#define MD(TA, TW) moe_down_kernel<TA, TW><<<grid, 128, smem, stream>>>((const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top)
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MD(float, float); else MD(float, bf16); }
+    else { if (w_dtype == TL_F32) MD(bf16, float); else MD(bf16, bf16); }
+#undef MD
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ experts, many tokens
+// Counting sort of the P = T * top pairs by expert, one block: offsets[e] .. offsets[e + 1] is expert e's run of
+// sorted places; place_of[pair] is where the pair went, pair_at[place] the pair there.  The order inside a run is
+// the order of the pairs (a thread takes a contiguous range of pairs and the ranges are placed in thread order), so
+// the same step sorts the same way every time.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ offsets,
+                                                        int* __restrict__ place_of, int* __restrict__ pair_at) {
+    extern __shared__ int cnt[];                         // [E][blockDim.x + 1] would be too much: counts per (expert, warp)
+    const int nw = blockDim.x >> 5, wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* base = cnt + E * nw;                            // [E + 1]
+    for (int i = threadIdx.x; i < E * nw; i += blockDim.x) cnt[i] = 0;
+    __syncthreads();
+    const int per = (P + nw - 1) / nw, lo = wid * per, hi = min(P, lo + per);      // a warp's contiguous range of pairs
+    for (int p = lo + lane; p < hi; p += 32) atomicAdd(&cnt[idx[p] * nw + wid], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            base[e] = run;
+            for (int w = 0; w < nw; ++w) { const int c = cnt[e * nw + w]; cnt[e * nw + w] = run; run += c; }
+        }
+        base[E] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = base[e];
+    // inside a warp's range: pairs in order, 32 at a time, ranked by a ballot per expert value
+    for (int p0 = lo; p0 < hi; p0 += 32) {
+        const int p = p0 + lane;
+        const int e = p < hi ? idx[p] : -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        int start = 0;
+        if (e >= 0) start = cnt[e * nw + wid];
+        __syncwarp();
+        if (e >= 0) {
+            const int place = start + rank;
+            place_of[p] = place;
+            pair_at[place] = p;
+            if (rank == __popc(same) - 1) cnt[e * nw + wid] = start + rank + 1;
+        }
+        __syncwarp();
+    }
+}
+
+TL_EXPORT int tl_moe_sort(const int* idx, int P, int E, int* offsets, int* place_of, int* pair_at, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    const size_t smem = ((size_t)E * 32 + E + 1) * sizeof(int);
+    if (smem > 48 * 1024) return 1;
+    moe_sort_kernel<<<1, 1024, smem, stream>>>(idx, P, E, offsets, place_of, pair_at);
+    return tl_launch_status();
+}
+
+// rows[place, :] = h[pair_at[place] / top, :]
+template <typename TA>
+__global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restrict__ pair_at, TA* __restrict__ rows, int K, int top) {
+    const size_t src = (size_t)(pair_at[blockIdx.x] / top) * K, dst = (size_t)blockIdx.x * K;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) rows[dst + k] = h[src + k];
+}
+
+TL_EXPORT int tl_moe_gather(const void* h, int act_dtype, const int* pair_at, void* rows, int P, int K, int top, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    if (act_dtype == TL_F32) moe_gather_kernel<float><<<P, 256, 0, stream>>>((const float*)h, pair_at, (float*)rows, K, top);
+    else moe_gather_kernel<bf16><<<P, 256, 0, stream>>>((const bf16*)h, pair_at, (bf16*)rows, K, top);
+    return tl_launch_status();
+}
+
+// u = relu(u)^2 in place
+template <typename TA>
+__global__ void relu_square_kernel(TA* __restrict__ u, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f<TA>(u[i]), 0.f);
+        u[i] = from_f<TA>(v * v);
+    }
+}
+
+TL_EXPORT int tl_relu_square(void* u, int act_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < (long long)tl_num_sms() * 16 ? (n + 255) / 256 : (long long)tl_num_sms() * 16);
+    if (act_dtype == TL_F32) relu_square_kernel<float><<<blocks, 256, 0, stream>>>((float*)u, (size_t)n);
+    else relu_square_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)u, (size_t)n);
+    return tl_launch_status();
+}
+
+// y[t, :] = sum_j wts[t, j] * rows[place_of[t * top + j], :], j in the order chosen
+template <typename TA>
+__global__ void moe_combine_kernel(const TA* __restrict__ rows, const int* __restrict__ place_of, const float* __restrict__ wts,
+                                   TA* __restrict__ y, int N, int top) {
+    const int t = blockIdx.x;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j)
+            acc = fmaf(wts[(size_t)t * top + j], to_f<TA>(rows[(size_t)place_of[(size_t)t * top + j] * N + n]), acc);
+        y[(size_t)t * N + n] = from_f<TA>(acc);
+    }
+}
+
+TL_EXPORT int tl_moe_combine(const void* rows, int act_dtype, const int* place_of, const float* wts, void* y, int T, int N,
+                             int top, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (act_dtype == TL_F32) moe_combine_kernel<float><<<T, 256, 0, stream>>>((const float*)rows, place_of, wts, (float*)y, N, top);
+    else moe_combine_kernel<bf16><<<T, 256, 0, stream>>>((const bf16*)rows, place_of, wts, (bf16*)y, N, top);
+    return tl_launch_status();
+}

@@ -14,9 +14,11 @@ import torch
 
 from ..config.base import ConfigError, architecture_name, read_config_json
 from ..config.qwen2 import Qwen2Config
+from ..config.vutesun import VutesunConfig
 from ..parts import Runtime
 from ..weights import load_weights
 from .qwen2 import describe_qwen2
+from .vutesun import describe_vutesun
 from .spec import Model
 
 
@@ -45,6 +47,7 @@ def registered_architectures() -> list:
 
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config, describe_qwen2)
+register_architecture("Vutesun", VutesunConfig, describe_vutesun)
 
 
 def load_config(folder):

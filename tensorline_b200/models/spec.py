@@ -93,9 +93,19 @@ class Model:
         for i, e in enumerate(self.spec.run):
             if e.reads_cache_of is None:
                 need = self.blocks[e.layer].cache_need()
-                if need is not None:
+                if isinstance(need, dict):               # a mixer made of several: one cache each, id (entry, name)
+                    for name, n in need.items():
+                        needs[(i, name)] = n
+                elif need is not None:
                     needs[i] = need
         return needs
+
+    def _cache_of(self, i: int, caches: dict):
+        """What run entry i's block is handed: its view, or {name: view} for a block whose mixer keeps several."""
+        need = self.blocks[self.spec.run[i].layer].cache_need()
+        if isinstance(need, dict):
+            return {name: caches[(i, name)] for name in need}
+        return caches.get(i)
 
     def graph_capturable(self) -> bool:
         """Whether a step of single tokens can be captured in a CUDA graph: every part reads the step from
@@ -114,9 +124,9 @@ class Model:
         pending = None
         for i, e in enumerate(self.spec.run):
             if e.reads_cache_of is None:
-                cache = caches.get(i)
+                cache = self._cache_of(i, caches)
             else:
-                owner = caches[e.reads_cache_of]
+                owner = self._cache_of(e.reads_cache_of, caches)
                 cache = KVCacheView(owner.k, owner.v, owner.group, owner=False) if isinstance(owner, KVCacheView) else owner
             pending = self.blocks[e.layer].forward(x, pending, ctx, cache)
         if ctx.want_rows.numel() == 0:

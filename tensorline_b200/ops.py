@@ -13,20 +13,34 @@ import torch
 
 from .csrc.build import CHECK_BUILD, load_library
 
-CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu", "recurrent.cu", "moe.cu"]
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 _SIGNATURES = {
     "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
-    "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _P],
+    "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _F, _I, _P],
     "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong,
                          _I, _P, _P, _F, _I, _I, _P, _P],
-    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _I, _P, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
     "tl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "tl_linear_scan": [_P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P, _F, _F, _P, ctypes.c_longlong, _P, _P, _P, _I, _I,
+                       _I, _I, _F, _P],
+    "tl_scan_state_floats": [_I, _I],
+    "tl_scan_columns": [],
+    "tl_head_norm_gate": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
+    "tl_sum_normed": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _F, _P],
+    "tl_small_proj": [_P, _I, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
+    "tl_topk_softmax": [_P, _I, _I, _P, _P, _I, _P],
+    "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
+    "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tl_moe_sort": [_P, _I, _I, _P, _P, _P, _P],
+    "tl_moe_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "tl_relu_square": [_P, _I, ctypes.c_longlong, _P],
+    "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
 }
 
 
@@ -231,9 +245,11 @@ def embed(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
 
 
 def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: torch.Tensor, eps: float,
-                rows: torch.Tensor | None = None, write_x: bool = True, pieces: torch.Tensor | None = None) -> None:
-    """x += r (if r), out = cast(x * rstd) * w.  x float32 [*, H]; r, out of the activation
-    type; `rows` picks the rows (x is then left alone).  `pieces` [S, rows of x, H] float32 instead
+                rows: torch.Tensor | None = None, write_x: bool = True, pieces: torch.Tensor | None = None,
+                alpha: float = 1.0, cast_first: bool = True) -> None:
+    """x += alpha * r (if r), out = cast(x * rstd) * w.  x float32 [*, H]; r, out of the activation
+    type; `rows` picks the rows (x is then left alone).  `cast_first` False: the norm stays float up to
+    the weight and only the result is rounded.  `pieces` [S, rows of x, H] float32 instead
     of r: the addend as a split-K product left it; summed in split order and rounded to the
     activation type inside the kernel (needs H % 4 == 0 and H <= 32768)."""
     H = x.shape[-1]
@@ -261,7 +277,8 @@ def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: t
     elif x.shape[0] != R:
         raise KernelError("add_rmsnorm: out must have x's rows")
     _check(core().tl_add_rmsnorm(_ptr(x), _ptr(r), _ptr(w), dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype),
-                                 _ptr(rows), R, H, float(eps), int(write_x), _ptr(pieces), splits, plane, _stream()),
+                                 _ptr(rows), R, H, float(eps), int(write_x), _ptr(pieces), splits, plane, float(alpha),
+                                 int(cast_first), _stream()),
            "add_rmsnorm")
 
 
@@ -327,8 +344,9 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tenso
 
 def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                    table: torch.Tensor, page_size: int, pos: torch.Tensor, req_slot: torch.Tensor,
-                   nq: int, nkv: int, d: int, window: int | None, scale: float) -> None:
-    """Exact-order paged attention; q rows `q_stride` elements apart, out [T, nq*d]."""
+                   nq: int, nkv: int, d: int, window: int | None, scale: float, sink: torch.Tensor | None = None) -> None:
+    """Exact-order paged attention; q rows `q_stride` elements apart, out [T, nq*d].  `sink` (float32 [nq]): one more
+    term exp(sink[h]) in every softmax denominator of head h."""
     T = out.shape[0]
     if out.shape[1] != nq * d or out.dtype != q.dtype or k_pages.dtype != q.dtype:
         raise KernelError("attn_tokenwise: out must be [T, nq*d] and all tensors of one type")
@@ -336,10 +354,16 @@ def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: t
         raise KernelError(f"attn_tokenwise: head_dim {d} > 512 is not supported")
     _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages")
     _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
+    _sink(sink, nq, "attn_tokenwise")
     _check(core().tl_attn_tokenwise(_ptr(q), q_stride, _ptr(out), dtype_code(q.dtype), _ptr(k_pages), _ptr(v_pages),
                                     _ptr(table), table.shape[1], page_size, _ptr(pos), _ptr(req_slot), T, nq, nkv, d,
-                                    int(window or 0), float(scale), table.shape[0], k_pages.shape[0], fault_words(out.device),
+                                    int(window or 0), float(scale), _ptr(sink), table.shape[0], k_pages.shape[0], fault_words(out.device),
                                     _stream()), "attn_tokenwise")
+
+
+def _sink(sink, nq: int, who: str) -> None:
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nq or not sink.is_contiguous()):
+        raise KernelError(f"{who}: sink must be float32 [query heads]")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> None:
@@ -385,3 +409,180 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
     _ints(out, "out")
     _check(core().tl_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_p), _ptr(uniform),
                             _ptr(out), _stream()), "sample")
+
+
+# ---------------------------------------------------------------------------------------------
+# Linear recurrences with a matrix state per head (csrc/recurrent.cu)
+
+def scan_state_floats(d: int, gated: bool) -> int:
+    """Floats of state that `linear_scan` keeps per (head, slice of `scan_columns()` value columns) for heads of d rows."""
+    n = core().tl_scan_state_floats(int(d), int(gated))
+    if n <= 0:
+        raise KernelError(f"linear_scan: heads of {d} rows are not supported (at most 256)")
+    return n
+
+
+def scan_columns() -> int:
+    return core().tl_scan_columns()
+
+
+def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, H: int, d: int, dv: int, state: torch.Tensor,
+                q_start: torch.Tensor, slots: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, *, B: int,
+                decay: torch.Tensor | None = None, gates: torch.Tensor | None = None, cap: float = 1.0,
+                inv_freq: torch.Tensor | None = None, rot: int = 0, pairing: str = "half", q_scale: float = 1.0,
+                k_scale: float = 1.0, den_eps: float = 0.0) -> None:
+    """S_t = a_t S_(t-1) + b_t k_t v_t^T and o_t = S_t^T q_t per (request, head), tokens of a request in order, the state
+    read from and left in `state[slot]` (float32, one row a slot, in the kernel's own layout: `scan_state_floats`).
+    q, k [H, d] and v [H, dv] of token t are at `proj[t, q_off:]`, `proj[t, k_off:]`, `proj[t, v_off:]`.
+    `decay` (float32 [H]): a_t = decay[h], b_t = 1.  `gates` (float32 [T, 2H], input then forget pre-activations): the
+    capped log gates with a running maximum, a normaliser, and o_t divided by max(|n_t . q_t|, exp(-m_t)) + den_eps.
+    q and k are rotated by `pos` over their first `rot` dimensions (`inv_freq` float32 [rot/2]) and scaled.  out float32
+    [T, H * dv]."""
+    T = proj.shape[0]
+    if (decay is None) == (gates is None):
+        raise KernelError("linear_scan: either a fixed decay per head or gate pre-activations")
+    _contig(proj, "proj"); _ints(q_start, "q_start"); _ints(slots, "slots"); _ints(pos, "pos"); _contig(state, "state"); _contig(out, "out")
+    if out.dtype != torch.float32 or out.shape != (T, H * dv) or state.dtype != torch.float32:
+        raise KernelError("linear_scan: out must be float32 [T, H * dv] and the state float32")
+    nz = -(-dv // scan_columns())
+    per_slot = H * nz * scan_state_floats(d, gates is not None)
+    if state[0].numel() != per_slot:
+        raise KernelError(f"linear_scan: a slot holds {state[0].numel()} floats, these sizes need {per_slot}")
+    for name, off, width in (("q", q_off, H * d), ("k", k_off, H * d), ("v", v_off, H * dv)):
+        if off < 0 or off + width > proj.shape[1]:
+            raise KernelError(f"linear_scan: {name} does not lie inside a projection row")
+    if decay is not None and (decay.dtype != torch.float32 or decay.numel() != H):
+        raise KernelError("linear_scan: decay must be float32 [H]")
+    if gates is not None and (gates.dtype != torch.float32 or gates.shape != (T, 2 * H) or not gates.is_contiguous()):
+        raise KernelError("linear_scan: gates must be float32 [T, 2H]")
+    if rot and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2):
+        raise KernelError("linear_scan: inv_freq must be float32 [rot/2]")
+    if pairing not in ("half", "interleaved"):
+        raise KernelError(f"linear_scan: pairing {pairing!r} is neither 'half' nor 'interleaved'")
+    _check(core().tl_linear_scan(_ptr(proj), dtype_code(proj.dtype), proj.shape[1], q_off, k_off, v_off, _ptr(gates), float(cap),
+                                 _ptr(decay), _ptr(inv_freq) if rot else None, int(rot), int(pairing == "interleaved"), _ptr(pos),
+                                 float(q_scale), float(k_scale), _ptr(state), per_slot, _ptr(q_start), _ptr(slots), _ptr(out),
+                                 int(B), H, d, dv, float(den_eps), _stream()), "linear_scan")
+
+
+_ACTS = {None: 0, "sigmoid": 1, "silu": 2}
+
+
+def head_norm_gate(o: torch.Tensor, out: torch.Tensor, H: int, dv: int, eps: float, weight: torch.Tensor | None = None,
+                   gate: torch.Tensor | None = None, gate_off: int = 0, act: str | None = None) -> None:
+    """out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[h, :] * act(gate[t, gate_off + h dv + :]); o float32
+    [T, H dv], out and gate rows of the activation type; weight (any float type, [H dv]) and the gate are optional."""
+    T = o.shape[0]
+    if o.dtype != torch.float32 or o.shape != (T, H * dv) or out.shape != o.shape:
+        raise KernelError("head_norm_gate: o must be float32 [T, H dv] and out of its shape")
+    if act not in _ACTS or (act is not None) != (gate is not None):
+        raise KernelError("head_norm_gate: a gate comes with 'sigmoid' or 'silu'")
+    _contig(o, "o"); _contig(out, "out")
+    g_ptr, g_stride = None, 0
+    if gate is not None:
+        if gate.dtype != out.dtype or gate.stride(1) != 1 or gate_off + H * dv > gate.shape[1]:
+            raise KernelError("head_norm_gate: the gate rows must be of out's type and hold H dv columns from gate_off")
+        g_ptr, g_stride = _ptr(gate) + gate_off * gate.element_size(), gate.stride(0)
+    if weight is not None and (weight.numel() != H * dv or not weight.is_contiguous()):
+        raise KernelError("head_norm_gate: weight must be [H dv]")
+    _check(core().tl_head_norm_gate(_ptr(o), g_ptr, g_stride, _ptr(weight), dtype_code(weight.dtype) if weight is not None else 0,
+                                    _ptr(out), dtype_code(out.dtype), T, H, dv, float(eps), _ACTS[act], _stream()), "head_norm_gate")
+
+
+def sum_normed(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, out: torch.Tensor, eps: float,
+               scale: float) -> None:
+    """out = scale * (a / rms(a) * wa + b / rms(b) * wb), rows of the model width; statistics in float32."""
+    T, W = a.shape
+    if b.shape != a.shape or out.shape != a.shape or b.dtype != a.dtype or out.dtype != a.dtype or wa.dtype != wb.dtype \
+            or wa.numel() != W or wb.numel() != W:
+        raise KernelError("sum_normed: a, b, out [T, W] of one type, weights [W] of one type")
+    _contig(a, "a"); _contig(b, "b"); _contig(out, "out"); _contig(wa, "wa"); _contig(wb, "wb")
+    _check(core().tl_sum_normed(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), dtype_code(wa.dtype), _ptr(out), dtype_code(out.dtype),
+                                T, W, float(eps), float(scale), _stream()), "sum_normed")
+
+
+# ---------------------------------------------------------------------------------------------
+# Routed feed-forward (csrc/moe.cu)
+
+def small_proj(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out[t, n] = bias[n] + h[t, :] . w[n, :] in float32 whatever h's type (router logits, gate pre-activations);
+    out may be a column range of a wider float32 tensor."""
+    T, K = h.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (T, N) or out.dtype != torch.float32 or out.stride(1) != 1 or h.stride(1) != 1:
+        raise KernelError("small_proj: h [T, K], w [N, K], out float32 [T, N]")
+    if bias is not None and (bias.dtype != w.dtype or bias.numel() != N):
+        raise KernelError("small_proj: bias must be [N] of w's type")
+    _contig(w, "w")
+    _check(core().tl_small_proj(_ptr(h), dtype_code(h.dtype), h.stride(0), _ptr(w), _ptr(bias), dtype_code(w.dtype), _ptr(out),
+                                out.stride(0), T, N, K, _stream()), "small_proj")
+
+
+def topk_softmax(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor) -> None:
+    """Per row of z (float32 [T, E]): the `top` largest entries (lowest index first on a tie) in idx int32 [T, top] and
+    the softmax over those entries alone in wts float32 [T, top]."""
+    T, E = z.shape
+    if z.dtype != torch.float32 or wts.dtype != torch.float32 or idx.shape != (T, top) or wts.shape != (T, top):
+        raise KernelError("topk_softmax: z float32 [T, E], idx int32 [T, top], wts float32 [T, top]")
+    _contig(z, "z"); _ints(idx, "idx"); _contig(wts, "wts")
+    _check(core().tl_topk_softmax(_ptr(z), E, int(top), _ptr(idx), _ptr(wts), T, _stream()), "topk_softmax")
+
+
+def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tensor) -> None:
+    """a[t * top + j, :] = relu(w_up[idx[t, j]] h[t])^2; w_up [E, F, K], a [T * top, F] of h's type."""
+    T, K = h.shape
+    E, F, _ = w_up.shape
+    top = idx.shape[1]
+    if w_up.shape[2] != K or a.shape != (T * top, F) or a.dtype != h.dtype:
+        raise KernelError("moe_up: w_up [E, F, K], a [T top, F] of h's type")
+    _contig(h, "h"); _contig(w_up, "w_up"); _ints(idx, "idx"); _contig(a, "a")
+    _check(core().tl_moe_up(_ptr(h), dtype_code(h.dtype), _ptr(w_up), dtype_code(w_up.dtype), _ptr(idx), _ptr(a), T * top, K, F,
+                            top, _stream()), "moe_up")
+
+
+def moe_down(a: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t] = sum_j wts[t, j] * w_down[idx[t, j]] a[t * top + j]; w_down [E, N, F]."""
+    T, top = idx.shape
+    E, N, F = w_down.shape
+    if a.shape != (T * top, F) or y.shape != (T, N) or y.dtype != a.dtype or wts.dtype != torch.float32 or wts.shape != idx.shape:
+        raise KernelError("moe_down: a [T top, F], w_down [E, N, F], y [T, N], wts float32 [T, top]")
+    _contig(a, "a"); _contig(w_down, "w_down"); _ints(idx, "idx"); _contig(wts, "wts"); _contig(y, "y")
+    _check(core().tl_moe_down(_ptr(a), dtype_code(a.dtype), _ptr(w_down), dtype_code(w_down.dtype), _ptr(idx), _ptr(wts), _ptr(y),
+                              T, F, N, top, _stream()), "moe_down")
+
+
+def moe_sort(idx: torch.Tensor, E: int):
+    """Pairs (token, chosen expert) sorted by expert: (offsets int32 [E + 1], place_of int32 [P], pair_at int32 [P])."""
+    P = idx.numel()
+    _ints(idx, "idx")
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=idx.device)
+    place_of = torch.empty(P, dtype=torch.int32, device=idx.device)
+    pair_at = torch.empty(P, dtype=torch.int32, device=idx.device)
+    _check(core().tl_moe_sort(_ptr(idx), P, E, _ptr(offsets), _ptr(place_of), _ptr(pair_at), _stream()), "moe_sort")
+    return offsets, place_of, pair_at
+
+
+def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, top: int, rows: torch.Tensor) -> None:
+    """rows[place] = h[pair_at[place] // top]."""
+    P, K = rows.shape
+    if h.shape[1] != K or rows.dtype != h.dtype or pair_at.numel() != P:
+        raise KernelError("moe_gather: rows [P, K] of h's type")
+    _contig(h, "h"); _contig(rows, "rows"); _ints(pair_at, "pair_at")
+    _check(core().tl_moe_gather(_ptr(h), dtype_code(h.dtype), _ptr(pair_at), _ptr(rows), P, K, int(top), _stream()), "moe_gather")
+
+
+def relu_square(u: torch.Tensor) -> None:
+    """u = relu(u)^2 in place."""
+    _contig(u, "u")
+    _check(core().tl_relu_square(_ptr(u), dtype_code(u.dtype), u.numel(), _stream()), "relu_square")
+
+
+def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, wts: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t] = sum_j wts[t, j] * rows[place_of[t * top + j]]."""
+    T, top = wts.shape
+    N = y.shape[1]
+    if rows.shape != (T * top, N) or rows.dtype != y.dtype or y.shape[0] != T or wts.dtype != torch.float32:
+        raise KernelError("moe_combine: rows [T top, N] of y's type, wts float32 [T, top]")
+    _contig(rows, "rows"); _ints(place_of, "place_of"); _contig(wts, "wts"); _contig(y, "y")
+    _check(core().tl_moe_combine(_ptr(rows), dtype_code(rows.dtype), _ptr(place_of), _ptr(wts), _ptr(y), T, N, top, _stream()),
+           "moe_combine")

@@ -12,6 +12,13 @@ The number of heads, of KV heads, the head size, the biases, the window, the pos
 (`qk_norm_eps`; weights `q_norm.weight`, `k_norm.weight` of the head size) are parameters; the
 fused kernel takes all of them as arguments.  A run entry that reads another entry's cache
 (`cache.owner` false) computes its own queries and writes no keys or values.
+
+Further parameters: `sink` (a learned number per query head, tensor `sink`: every softmax denominator of the
+head also holds exp(sink), a term without key or value that is not scaled), `v_head_dim` (values of another size
+than queries and keys) and `names` (the tensors' names under the mixer's prefix).  The kernels and the pages work
+on one head size: with `v_head_dim` != `head_dim`, or a size the bfloat16 kernels do not take, the smaller of
+q/k and v is padded with zero rows in the stacked projection (and zero columns in the output projection), which
+changes no score and no output.
 """
 from __future__ import annotations
 
@@ -22,6 +29,20 @@ from ..cache import PagedKV
 from .base import POSITION_ENCODINGS, Part, PartSpec, Rotary, Runtime, TensorSpec, register_mixer
 from .linear import SplitSum, matmul
 
+_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+          "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sink"}
+
+
+def _pad_heads(t: torch.Tensor, heads: int, size: int, to: int) -> torch.Tensor:
+    """[heads * size, ...] -> [heads * to, ...] with zeros behind every head's rows."""
+    if size == to:
+        return t
+    rest = t.shape[1:]
+    out = torch.zeros((heads, to) + tuple(rest), dtype=t.dtype, device=t.device)
+    out[:, :size] = t.reshape((heads, size) + tuple(rest))
+    return out.reshape((heads * to,) + tuple(rest))
+
 
 @register_mixer("paged_attention")
 class PagedAttention(Part):
@@ -30,46 +51,62 @@ class PagedAttention(Part):
 
     def __init__(self, rt: Runtime, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, window: int | None = None, scale: float | None = None,
-                 qk_norm_eps: float | None = None):
+                 qk_norm_eps: float | None = None, v_head_dim: int | None = None, sink: bool = False,
+                 names: dict | None = None):
         super().__init__(rt)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
-        if head_dim % 16 and not rt.exact:
-            raise ValueError(f"head_dim {head_dim}: the bfloat16 attention kernels take multiples of 16")
-        self.hidden, self.nq, self.nkv, self.d = hidden, num_heads, num_kv_heads, head_dim
+        self.dk = head_dim
+        self.dv = head_dim if v_head_dim is None else v_head_dim
+        d = max(self.dk, self.dv)
+        if not rt.exact:
+            d = -(-d // 16) * 16                          # the bfloat16 attention kernels take multiples of 16
+        if d != self.dk and qk_norm_eps is not None:
+            raise ValueError("a q/k norm over a padded head is not supported")
+        self.hidden, self.nq, self.nkv, self.d = hidden, num_heads, num_kv_heads, d
         self.qkv_bias, self.window = qkv_bias, window
         self.scale = head_dim ** -0.5 if scale is None else scale          # tensorline/paged.py:119
         self.position = POSITION_ENCODINGS.build(position, rt, head_dim=head_dim)
         self.qk_norm_eps = qk_norm_eps
-        self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.has_sink = bool(sink)
+        self.names = {**_NAMES, **(names or {})}
+        self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = self.sink = None
 
     def cache_need(self):
         return PagedKV(self.nkv, self.d, self.window)
 
     def expected_tensors(self, prefix):
-        H, nq, nkv, d = self.hidden, self.nq, self.nkv, self.d
-        out = {f"{prefix}.q_proj.weight": TensorSpec((nq * d, H)), f"{prefix}.k_proj.weight": TensorSpec((nkv * d, H)),
-               f"{prefix}.v_proj.weight": TensorSpec((nkv * d, H)), f"{prefix}.o_proj.weight": TensorSpec((H, nq * d))}
+        H, nq, nkv, dk, dv = self.hidden, self.nq, self.nkv, self.dk, self.dv
+        n = {k: f"{prefix}.{v}" for k, v in self.names.items()}
+        out = {n["q"]: TensorSpec((nq * dk, H)), n["k"]: TensorSpec((nkv * dk, H)),
+               n["v"]: TensorSpec((nkv * dv, H)), n["o"]: TensorSpec((H, nq * dv))}
         if self.qkv_bias:
-            out.update({f"{prefix}.q_proj.bias": TensorSpec((nq * d,)), f"{prefix}.k_proj.bias": TensorSpec((nkv * d,)),
-                        f"{prefix}.v_proj.bias": TensorSpec((nkv * d,))})
+            out.update({n["q_bias"]: TensorSpec((nq * dk,)), n["k_bias"]: TensorSpec((nkv * dk,)),
+                        n["v_bias"]: TensorSpec((nkv * dv,))})
         if self.qk_norm_eps is not None:
-            out.update({f"{prefix}.q_norm.weight": TensorSpec((d,), init="ones"),
-                        f"{prefix}.k_norm.weight": TensorSpec((d,), init="ones")})
+            out.update({n["q_norm"]: TensorSpec((dk,), init="ones"), n["k_norm"]: TensorSpec((dk,), init="ones")})
+        if self.has_sink:
+            out[n["sink"]] = TensorSpec((nq,))
         return out
 
     def bind(self, weights, prefix):
-        w = [weights[f"{prefix}.{n}_proj.weight"] for n in "qkv"]
-        self.w_qkv = self._compute_copy(torch.cat(w, dim=0))
+        nq, nkv, dk, dv, d = self.nq, self.nkv, self.dk, self.dv, self.d
+        n = {k: f"{prefix}.{v}" for k, v in self.names.items()}
+        heads = (("q", nq, dk), ("k", nkv, dk), ("v", nkv, dv))
+        self.w_qkv = self._compute_copy(torch.cat([_pad_heads(weights[n[k]], h, size, d) for k, h, size in heads], dim=0))
         if self.qkv_bias:
-            b = [weights[f"{prefix}.{n}_proj.bias"] for n in "qkv"]
-            self.b_qkv = torch.cat(b, dim=0).contiguous()
+            self.b_qkv = torch.cat([_pad_heads(weights[n[k + "_bias"]], h, size, d) for k, h, size in heads], dim=0).contiguous()
             if self.b_qkv.dtype not in (torch.float32, torch.bfloat16):
                 self.b_qkv = self.b_qkv.float()
-        self.w_o = self._compute_copy(weights[f"{prefix}.o_proj.weight"])
+        w_o = weights[n["o"]]                            # [H, nq * dv]: zero columns behind every head's values
+        if dv != d:
+            w_o = _pad_heads(w_o.t().contiguous(), nq, dv, d).t()
+        self.w_o = self._compute_copy(w_o)
         if self.qk_norm_eps is not None:
-            self.q_norm = weights[f"{prefix}.q_norm.weight"].float().contiguous()
-            self.k_norm = weights[f"{prefix}.k_norm.weight"].float().contiguous()
+            self.q_norm = weights[n["q_norm"]].float().contiguous()
+            self.k_norm = weights[n["k_norm"]].float().contiguous()
+        if self.has_sink:
+            self.sink = weights[n["sink"]].float().contiguous()
 
     def forward(self, h, ctx, cache):
         nq, nkv, d = self.nq, self.nkv, self.d
@@ -95,7 +132,7 @@ class PagedAttention(Part):
         # (the TMA decode kernel) needs no rotary kernel in front of it.
         fold = None
         if (ctx.decode_only and not ctx.force_exact_attention and qkv.dtype == torch.bfloat16 and pieces is None and plain
-                and rot == d and self._folds_rope(ctx)):
+                and rot == d and self.sink is None and self._folds_rope(ctx)):
             fold = {"inv_freq": inv_freq, "bias": self.b_qkv, "write_kv": cache.owner, "unfold": rotary_kernel}
         else:
             rotary_kernel()

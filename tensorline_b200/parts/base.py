@@ -18,7 +18,8 @@ Interfaces (all tensors on the device; T tokens of the step flattened on axis 0)
                   be a no-op (`rot` = 0).
 * Mixer           `cache_need() -> PagedKV | SlotState | None`; `forward(h, ctx, cache) -> y`;
                   `cache` is what the cache manager keeps for this run entry (`KVCacheView`,
-                  `StateView` or None), `ctx` the step's `StepContext`.
+                  `StateView` or None), `ctx` the step's `StepContext`.  A mixer made of several
+                  (`cache_need()` -> {name: need}) gets {name: view}.
 * FeedForward     `forward(h, ctx) -> y`.
 * Block           `forward(x, pending, ctx, cache) -> pending`: runs its norms, mixer and
                   feed-forward; the sum into the residual stream x happens inside the norms.
@@ -58,6 +59,12 @@ class Runtime:
     @property
     def exact(self) -> bool:
         return self.act_dtype == torch.float32
+
+
+def tensor_name(prefix: str, suffix: str) -> str:
+    """Name of a part's tensor: `prefix.suffix`, or the prefix itself for a part whose one tensor carries the
+    part's own name (`suffix` empty)."""
+    return f"{prefix}.{suffix}" if suffix else prefix
 
 
 class Part:
@@ -153,4 +160,4 @@ class StateView:
 __all__ = ["PartSpec", "Runtime", "Part", "Registry", "Rotary", "NORMS", "POSITION_ENCODINGS", "MIXERS", "FEED_FORWARDS",
            "BLOCKS", "EMBEDDINGS", "HEADS", "register_norm", "register_position_encoding", "register_mixer",
            "register_feed_forward", "register_block", "register_embedding", "register_head", "KVCacheView",
-           "StateView", "TensorSpec"]
+           "StateView", "TensorSpec", "tensor_name"]

@@ -9,25 +9,30 @@ first norm (or the model's last) as `pending`.
 from __future__ import annotations
 
 from .base import FEED_FORWARDS, MIXERS, NORMS, Part, PartSpec, Runtime, register_block
+from .linear import Scaled
 
 
 @register_block("pre_norm")
 class PreNormBlock(Part):
-    def __init__(self, rt: Runtime, mixer: PartSpec, feed_forward: PartSpec, norm1: PartSpec, norm2: PartSpec,
-                 names: dict | None = None):
+    def __init__(self, rt: Runtime, mixer: PartSpec, feed_forward: PartSpec | None, norm1: PartSpec, norm2: PartSpec | None,
+                 names: dict | None = None, residual_scale: float = 1.0):
+        """`feed_forward` None: the layer is norm and mixer only.  `residual_scale`: each sub-block's output counts
+        that many times in the residual sum, x += scale * y."""
         super().__init__(rt)
         self.norm1 = NORMS.build(norm1, rt)
         self.mixer = MIXERS.build(mixer, rt)
-        self.norm2 = NORMS.build(norm2, rt)
-        self.ff = FEED_FORWARDS.build(feed_forward, rt)
+        self.norm2 = NORMS.build(norm2, rt) if feed_forward is not None else None
+        self.ff = FEED_FORWARDS.build(feed_forward, rt) if feed_forward is not None else None
+        self.residual_scale = float(residual_scale)
         # names of the sub-parts inside the layer's tensor prefix
         self.names = {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm",
                       "feed_forward": "mlp", **(names or {})}
 
     def _children(self, prefix):
         n = self.names
-        return ((self.norm1, f"{prefix}.{n['norm1']}"), (self.mixer, f"{prefix}.{n['mixer']}"),
-                (self.norm2, f"{prefix}.{n['norm2']}"), (self.ff, f"{prefix}.{n['feed_forward']}"))
+        parts = ((self.norm1, f"{prefix}.{n['norm1']}"), (self.mixer, f"{prefix}.{n['mixer']}"),
+                 (self.norm2, f"{prefix}.{n['norm2']}"), (self.ff, f"{prefix}.{n['feed_forward']}"))
+        return tuple((part, p) for part, p in parts if part is not None)
 
     def expected_tensors(self, prefix):
         out = {}
@@ -44,15 +49,20 @@ class PreNormBlock(Part):
 
     @property
     def graph_capturable(self) -> bool:
-        return all(part.graph_capturable for part in (self.norm1, self.mixer, self.norm2, self.ff))
+        return all(part.graph_capturable for part in (self.norm1, self.mixer, self.norm2, self.ff) if part is not None)
 
     def forward(self, x, pending, ctx, cache):
         # a norm that supports it hands a part that says it can take one (`accepts_normed_input`) the recipe of its
         # result instead of the result (see parts/linear.py)
         h = self._norm(self.norm1, x, pending, self.mixer)
-        a = self.mixer.forward(h, ctx, cache)
+        a = self._addend(self.mixer.forward(h, ctx, cache))
+        if self.ff is None:
+            return a
         h = self._norm(self.norm2, x, a, self.ff)
-        return self.ff.forward(h, ctx)
+        return self._addend(self.ff.forward(h, ctx))
+
+    def _addend(self, y):
+        return y if self.residual_scale == 1.0 else Scaled(y, self.residual_scale)
 
     @staticmethod
     def _norm(norm, x, pending, consumer):

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Part, Runtime, TensorSpec, register_embedding, register_head
+from .base import Part, Runtime, TensorSpec, register_embedding, register_head, tensor_name
 from .linear import matmul
 
 
@@ -12,16 +12,16 @@ from .linear import matmul
 class Embedding(Part):
     graph_capturable = True
 
-    def __init__(self, rt: Runtime, vocab: int, dim: int):
+    def __init__(self, rt: Runtime, vocab: int, dim: int, tensor: str = "weight"):
         super().__init__(rt)
-        self.vocab, self.dim = vocab, dim
+        self.vocab, self.dim, self.tensor = vocab, dim, tensor
         self.weight = None
 
     def expected_tensors(self, prefix):
-        return {f"{prefix}.weight": TensorSpec((self.vocab, self.dim))}
+        return {tensor_name(prefix, self.tensor): TensorSpec((self.vocab, self.dim))}
 
     def bind(self, weights, prefix):
-        self.weight = self._compute_copy(weights[f"{prefix}.weight"])
+        self.weight = self._compute_copy(weights[tensor_name(prefix, self.tensor)])
 
     def forward(self, ids):
         """The residual stream starts here, in float32."""
@@ -37,19 +37,19 @@ class LMHead(Part):
     graph_capturable = True
     accepts_normed_input = True         # `h` may be a `NormedInput`: the product normalises it on the fly
 
-    def __init__(self, rt: Runtime, vocab: int, dim: int, tied: bool):
+    def __init__(self, rt: Runtime, vocab: int, dim: int, tied: bool, tensor: str = "weight"):
         super().__init__(rt)
-        self.vocab, self.dim, self.tied = vocab, dim, tied
+        self.vocab, self.dim, self.tied, self.tensor = vocab, dim, tied, tensor
         self.weight = None
 
     def expected_tensors(self, prefix):
-        return {f"{prefix}.weight": TensorSpec((self.vocab, self.dim), optional=self.tied)}
+        return {tensor_name(prefix, self.tensor): TensorSpec((self.vocab, self.dim), optional=self.tied)}
 
     def bind(self, weights, prefix, embedding: Embedding | None = None):
         if self.tied:
             self.weight = embedding.weight
         else:
-            self.weight = self._compute_copy(weights[f"{prefix}.weight"])
+            self.weight = self._compute_copy(weights[tensor_name(prefix, self.tensor)])
 
     def forward(self, h):
         return matmul(h, self.weight, out_dtype=torch.float32)

@@ -107,8 +107,19 @@ class NormedInput:
         return h
 
 
+class Scaled:
+    """An addend of the residual stream that counts `alpha` times: x += alpha * value.  The norm that does the sum
+    multiplies on the way (one fused multiply-add in float32); anyone else calls `resolve`."""
+
+    def __init__(self, value, alpha: float):
+        self.value, self.alpha = resolve(value), float(alpha)
+        self.dtype, self.shape = self.value.dtype, self.value.shape
+
+
 def resolve(t):
     """A tensor from what a projection or a norm returned."""
+    if isinstance(t, Scaled):
+        return (t.value.float() * t.alpha).to(t.dtype)
     if isinstance(t, PendingProduct):
         t = t.run()
     if isinstance(t, NormedInput):

@@ -1,0 +1,91 @@
+"""Routed feed-forward (mixture of experts).
+
+    z = h Wr^T + br                      router logits, float32 in both engines
+    chosen: the `top` largest z;         weights = softmax over the chosen logits only
+    y = sum_j weight_j * Wdown[e_j] act(Wup[e_j] h)          experts without biases, act = relu(.)^2
+
+The experts' matrices are stacked ([E, F, K] and [E, K, F]) at load time.  Steps of few tokens stream, for every
+(token, chosen expert) pair, that expert's rows (`ops.moe_up`, `ops.moe_down`): nothing is sorted and nothing comes
+back to the host, so the step sits in a CUDA graph.  Steps of many tokens sort the pairs by expert on the device,
+gather the tokens' rows in that order and run two dense products per expert on its run of rows (the engine's own
+products: the library for bfloat16, the exact-order kernel for float32), which needs the runs' bounds on the host.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .. import ops
+from .base import Part, Runtime, TensorSpec, register_feed_forward
+from .linear import matmul, resolve
+
+# up to this many tokens a step the experts are streamed pair by pair
+STREAM_MAX_TOKENS = int(os.environ.get("TENSORLINE_B200_MOE_STREAM_MAX_TOKENS", 32))
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(Part):
+    graph_capturable = True              # steps of single tokens stay under STREAM_MAX_TOKENS rows... see forward
+
+    def __init__(self, rt: Runtime, hidden: int, inner: int, experts: int, top: int, activation: str = "relu_squared",
+                 router_bias: bool = True, names: dict | None = None):
+        super().__init__(rt)
+        if activation != "relu_squared":
+            raise ValueError(f"routed_experts runs 'relu_squared', not {activation!r}")
+        if not 1 <= top <= min(experts, 32) or experts > 1024:
+            raise ValueError(f"routed_experts: top {top} of {experts} experts is outside what the choice kernel takes")
+        self.hidden, self.inner, self.E, self.top, self.router_bias = hidden, inner, experts, top, router_bias
+        self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}", "up": "up", "down": "down", **(names or {})}
+        self.w_router = self.b_router = self.w_up = self.w_down = None
+
+    def _expert(self, prefix, e, which):
+        return f"{prefix}.{self.names['expert'].format(e)}.{self.names[which]}"
+
+    def expected_tensors(self, prefix):
+        out = {f"{prefix}.{self.names['router']}": TensorSpec((self.E, self.hidden))}
+        if self.router_bias:
+            out[f"{prefix}.{self.names['router_bias']}"] = TensorSpec((self.E,))
+        for e in range(self.E):
+            out[self._expert(prefix, e, "up")] = TensorSpec((self.inner, self.hidden))
+            out[self._expert(prefix, e, "down")] = TensorSpec((self.hidden, self.inner))
+        return out
+
+    def bind(self, weights, prefix):
+        self.w_router = weights[f"{prefix}.{self.names['router']}"].contiguous()
+        if self.router_bias:
+            self.b_router = weights[f"{prefix}.{self.names['router_bias']}"].to(self.w_router.dtype).contiguous()
+        self.w_up = self._compute_copy(torch.stack([weights[self._expert(prefix, e, "up")] for e in range(self.E)]))
+        self.w_down = self._compute_copy(torch.stack([weights[self._expert(prefix, e, "down")] for e in range(self.E)]))
+
+    def forward(self, h, ctx):
+        h = resolve(h)
+        T, top = h.shape[0], self.top
+        z = torch.empty((T, self.E), dtype=torch.float32, device=h.device)
+        ops.small_proj(h, self.w_router, self.b_router, z)
+        idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+        wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
+        ops.topk_softmax(z, top, idx, wts)
+        y = torch.empty((T, self.hidden), dtype=h.dtype, device=h.device)
+        if T <= STREAM_MAX_TOKENS or ctx.graph_max_ctx:
+            a = torch.empty((T * top, self.inner), dtype=h.dtype, device=h.device)
+            ops.moe_up(h, self.w_up, idx, a)
+            ops.moe_down(a, self.w_down, idx, wts, y)
+            return y
+        offsets, place_of, pair_at = ops.moe_sort(idx, self.E)
+        rows = torch.empty((T * top, self.hidden), dtype=h.dtype, device=h.device)
+        ops.moe_gather(h, pair_at, top, rows)
+        bounds = offsets.tolist()                        # the one read-back of the step: where every expert's run ends
+        inner = torch.empty((T * top, self.inner), dtype=h.dtype, device=h.device)
+        for e in range(self.E):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                inner[lo:hi] = matmul(rows[lo:hi], self.w_up[e])
+        ops.relu_square(inner)
+        outs = torch.empty((T * top, self.hidden), dtype=h.dtype, device=h.device)
+        for e in range(self.E):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                outs[lo:hi] = matmul(inner[lo:hi], self.w_down[e])
+        ops.moe_combine(outs, place_of, wts, y)
+        return y

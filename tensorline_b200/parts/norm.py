@@ -4,8 +4,8 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Part, Runtime, TensorSpec, register_norm
-from .linear import FUSE_NORMS, NormedInput, PendingProduct, SplitSum
+from .base import Part, Runtime, TensorSpec, register_norm, tensor_name
+from .linear import FUSE_NORMS, NormedInput, PendingProduct, Scaled, SplitSum, resolve
 
 
 @register_norm("rms_norm")
@@ -13,20 +13,36 @@ class RMSNorm(Part):
     graph_capturable = True
     can_defer = True                    # add_norm(..., defer=True) may return a `NormedInput`
 
-    def __init__(self, rt: Runtime, dim: int, eps: float):
+    def __init__(self, rt: Runtime, dim: int, eps: float, tensor: str = "weight", one_plus: bool = False,
+                 cast_first: bool = True):
+        """`tensor`: the weight's name under the norm's prefix ("": the prefix itself).  `one_plus`: the stored weight
+        lies around zero and the norm multiplies by 1 + w.  `cast_first` False: x * rstd * w in float32 and one
+        rounding at the end, instead of a rounding to the activation type before the weight."""
         super().__init__(rt)
         self.dim, self.eps = dim, eps
+        self.tensor, self.one_plus, self.cast_first = tensor, one_plus, cast_first
+        self.can_defer = cast_first and not one_plus         # the products that normalise on the fly round first
         self.weight = None
 
     def expected_tensors(self, prefix):
-        return {f"{prefix}.weight": TensorSpec((self.dim,), init="ones")}
+        return {tensor_name(prefix, self.tensor): TensorSpec((self.dim,), init="normal" if self.one_plus else "ones")}
 
     def bind(self, weights, prefix):
-        self.weight = weights[f"{prefix}.weight"].contiguous()      # stays in its stored type
+        w = weights[tensor_name(prefix, self.tensor)]
+        self.weight = (1.0 + w.float()).contiguous() if self.one_plus else w.contiguous()      # else in its stored type
 
     def add_norm(self, x, pending, rows=None, defer=False):
         """`defer`: the caller's next step is a product that takes a `NormedInput`."""
         n = x.shape[0] if rows is None else rows.numel()
+        if isinstance(pending, Scaled):                  # x += alpha * value
+            h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
+            ops.add_rmsnorm(x, pending.value, self.weight, h, self.eps, rows=rows, alpha=pending.alpha, cast_first=self.cast_first)
+            return h
+        if not self.cast_first:
+            pending = resolve(pending)
+            h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
+            ops.add_rmsnorm(x, pending, self.weight, h, self.eps, rows=rows, cast_first=False)
+            return h
         if isinstance(pending, PendingProduct):
             ssq = pending.add_into(x)                    # the product adds its result into x itself, where its plan allows
             if ssq is None:

@@ -16,6 +16,7 @@ from .base import Part, Rotary, Runtime, register_position_encoding
 @register_position_encoding("rotary_half")
 class RotaryHalf(Part):
     graph_capturable = True
+    pairing = "half"
 
     def __init__(self, rt: Runtime, head_dim: int, theta: float, rotary_dim: int | None = None):
         super().__init__(rt)
@@ -27,10 +28,16 @@ class RotaryHalf(Part):
         self.inv_freq = (float(theta) ** (-i / rot)).to(torch.float32).to(rt.device)
 
     def rotary(self):
-        return Rotary(self.inv_freq, self.rot, "half")
+        return Rotary(self.inv_freq, self.rot, self.pairing)
 
     def on_embedding(self, x, ctx):
         return None
+
+
+@register_position_encoding("rotary_interleaved")
+class RotaryInterleaved(RotaryHalf):
+    """The same table; pair i is dimensions (2i, 2i + 1)."""
+    pairing = "interleaved"
 
 
 @register_position_encoding("none")

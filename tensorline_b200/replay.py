@@ -1,6 +1,6 @@
 """Trace replay: feed given token ids through a model step by step and write logits.
 
-    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--graphs]
+    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--max-live N] [--graphs]
 
 Steps come on standard input, one JSON object a line:
 
@@ -12,7 +12,8 @@ in which logits are wanted, `OUT/<step>.f32` holds them as little-endian float32
 [wanted, vocab], in the order of the entries and of `want`.  After every step a line
 `done <step>` is printed and flushed.  `end` names the requests that are finished after the step;
 their pages and slots are given back and used again.  The cache pool holds `--max-tokens` tokens
-(each live request's count rounded up to whole pages), and not one page more.  With `--graphs`, a
+(each live request's count rounded up to whole pages), and not one page more, and `--max-live` request slots
+(block-table rows and state of fixed size), four unless told otherwise.  With `--graphs`, a
 step whose entries are all single tokens of running requests with `want` [0] (a decode step) is
 replayed from the CUDA graph of its batch-size bucket, as generation does; every other step runs
 as it is.
@@ -94,13 +95,16 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (rounded up per request to whole pages)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-live", type=int, default=4, help="request slots: the most requests that are live at any time")
     ap.add_argument("--graphs", action="store_true", help="replay decode steps from CUDA graphs, as generation does")
     a = ap.parse_args(argv)
     if a.page_size < 1 or 64 % a.page_size:
         ap.error("--page-size must divide 64")
     out = Path(a.out)
     out.mkdir(parents=True, exist_ok=True)
-    runner, _ = make_runner(a.model, a.dtype, a.max_tokens, page_size=a.page_size, graphs=a.graphs)
+    if a.max_live < 1:
+        ap.error("--max-live must be positive")
+    runner, _ = make_runner(a.model, a.dtype, a.max_tokens, page_size=a.page_size, max_live=a.max_live, graphs=a.graphs)
     session = TraceSession(runner)
     for line in sys.stdin:
         line = line.strip()
