@@ -88,6 +88,7 @@ struct AttnArgs {
     // stage landed, 4 block end, 5 last stage worked through, 6 at the cluster barrier, 7 past it
     TlTrace trace;
     bf16* k_pages_w; bf16* v_pages_w;
+    const float* sink;                 // [nq] or null: one more term exp(sink[h]) in every softmax denominator of head h
 };
 
 // Eight values at i0.. and the eight at D/2 + i0.. of one head's row: + bias, rotated (rotate-half pairs, angle of pair i in
@@ -383,6 +384,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
         lr += __shfl_xor_sync(0xffffffffu, lr, 2);
         const int R = row0 + warp * 16 + (lane >> 2) + r * 8;
         if (R >= rows_total) continue;
+        lr += tl_sink_term(A.sink, kh * g + R % g, m[r]);
         const float inv = lr > 0.f ? 1.0f / lr : 0.f;
         bf16* dst = A.out + ((size_t)(qs + R / g) * A.nq + (kh * g + R % g)) * D + (lane & 3) * 2;
 #pragma unroll
@@ -524,6 +526,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
         }
         const int head = kh * g + hg;
         if (A.splits == 1) {
+            lt += tl_sink_term(A.sink, head, mm);
             A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
         } else {
             const size_t pi = ((size_t)b * A.nq + head) * A.splits + split;
@@ -878,7 +881,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (CLUSTER) {
                 dst_o[row * cpc] = acc;
             } else if (A.splits == 1) {
-                const float lt = sLT[row];
+                const float lt = sLT[row] + tl_sink_term(A.sink, head, sMM[row]);
                 A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
             } else {
                 const size_t pi = ((size_t)b * A.nq + head) * A.splits + split;
@@ -919,6 +922,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     acc += f * os[sp]; lt += f * ls[sp];
                 }
             }
+            lt += tl_sink_term(A.sink, kh * g + row, mm);
             A.out[((size_t)qrow * A.nq + kh * g + row) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
         }
     }
@@ -947,6 +951,7 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
             const float ms = A.part_ml[(p0 + sp) * 2];
             lt += (ms == -INFINITY ? 0.f : exp2f(ms - mm)) * A.part_ml[(p0 + sp) * 2 + 1];
         }
+        lt += tl_sink_term(A.sink, head, mm);
         const float inv = lt > 0.f ? 1.0f / lt : 0.f;
         for (int col = threadIdx.x; col < D; col += blockDim.x) {
             float acc = 0.f;
@@ -981,7 +986,7 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
             if (sp < ns) wgt[sp] = f;
             lt += f * ls[k];
         }
-        lt = warp_sum(lt);
+        lt = warp_sum(lt) + tl_sink_term(A.sink, head, mm);
         if (lane == 0) inv_total = lt > 0.f ? 1.0f / lt : 0.f;
     }
     __syncthreads();
@@ -1015,6 +1020,11 @@ int set_attrs() {
 }  // namespace
 
 TL_EXPORT int tl_attn_head_dim() { return D; }
+
+// The sink of the launches that follow (device pointer, float [nq], or null for none), until it is set again: the
+// launchers set it before every launch, so the entry points keep their arguments.
+static const float* g_sink = nullptr;
+TL_EXPORT int tl_attn_set_sink(const float* sink) { g_sink = sink; return 0; }
 // 1 if this library was compiled as the checking build (-DTL_CHECK=1).
 TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 // Block-table entries a decode block may copy: chunk / page_size of a decode call may not exceed it.
@@ -1032,6 +1042,7 @@ TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void
     int e = set_attrs();
     if (e) return e;
     AttnArgs A{};
+    A.sink = g_sink;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
@@ -1058,6 +1069,7 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     int e = set_attrs();
     if (e) return e;
     AttnArgs A{};
+    A.sink = g_sink;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
@@ -1148,6 +1160,7 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
     if ((e = make_pages_map(&mk, k_pages, rows, page_size))) return e;
     if ((e = make_pages_map(&mv, v_pages, rows, page_size))) return e;
     AttnArgs A{};
+    A.sink = g_sink;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;

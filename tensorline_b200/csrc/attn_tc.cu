@@ -181,6 +181,7 @@ struct TcAttnArgs {
     // query tiles alone would leave most of the GPU idle.
     int ksplit, tokens;
     float* part_o; float* part_ml;
+    const float* sink;                 // [nq] or null: one more term exp(sink[h]) in every softmax denominator of head h
 };
 
 // One thread's share of a 128-row Q tile, 16-byte chunks r, r + 128, ... of its BM x D / 8 chunks; row = (token, head of
@@ -377,7 +378,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
         // ------------------------------------------------------------ epilogue: the last P V has finished
         if (ok && mbar_wait(bar_o + ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, abort_flag, A.status, 4)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float lt = l + tl_sink_term(A.sink, kh * g + R % g, m_ref);
+            const float inv = lt > 0.f ? 1.0f / lt : 0.f;
             bf16* dst = nullptr;
             if (R < rows_total) dst = A.out + ((size_t)(qs + R / g) * A.nq + (kh * g + R % g)) * D;
 #pragma unroll 1
@@ -748,7 +750,8 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         } else if (ok && n_mine > 0 &&
             mbar_wait(bar_o + t * 2 + ((n_mine - 1) & 1), ((n_mine - 1) >> 1) & 1, abort_flag, A.status, 4)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float lt = l + tl_sink_term(A.sink, kh * g + R % g, m_ref);
+            const float inv = lt > 0.f ? 1.0f / lt : 0.f;
             bf16* dst = nullptr;
             if (R < rows_total) dst = A.out + ((size_t)(qs + R / g) * A.nq + (kh * g + R % g)) * D;
 #pragma unroll 1
@@ -1059,7 +1062,8 @@ attn_tc3_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         // ------------------------------------------------------------ epilogue: the tile's last P V has finished
         if (ok && n_mine > 0 && mbar_wait(bar_o + t, (n_mine - 1) & 1, abort_flag, A.status, 4)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float lt = l + tl_sink_term(A.sink, kh * g + R % g, m_ref);
+            const float inv = lt > 0.f ? 1.0f / lt : 0.f;
             bf16* dst = nullptr;
             if (R < rows_total) dst = A.out + ((size_t)(qs + R / g) * A.nq + (kh * g + R % g)) * D;
 #pragma unroll 1
@@ -1204,6 +1208,11 @@ bool g_attr_done[TL_MAX_DEVICES] = {};
 }  // namespace
 
 TL_EXPORT int tl_attn_tc_head_dim() { return D; }
+
+// The sink of the launches that follow (device pointer, float [nq], or null for none), until it is set again: the
+// launchers set it before every launch, so the entry points keep their arguments.
+static const float* g_sink = nullptr;
+TL_EXPORT int tl_attn_set_sink(const float* sink) { g_sink = sink; return 0; }
 // 1 if this library was compiled as the checking build (-DTL_CHECK=1).
 TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 
@@ -1223,6 +1232,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
         g_attr_done[dev] = true;
     }
     TcAttnArgs A{};
+    A.sink = g_sink;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
@@ -1240,7 +1250,8 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
 // The parts that the runs of a split launch have left, merged: one (token, head) a group of D / 4 threads.  rows: the
 // tokens to merge (the step may hold tokens that another kernel serves).
 __global__ void attn_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                                     const int* __restrict__ rows, int n_rows, int tokens, int nq, int ksplit) {
+                                     const int* __restrict__ rows, int n_rows, int tokens, int nq, int ksplit,
+                                     const float* __restrict__ sink) {
     constexpr int PER = D / 4;                             // threads a (token, head)
     const size_t item = (size_t)blockIdx.x * (blockDim.x / PER) + threadIdx.x / PER;
     if (item >= (size_t)n_rows * nq) return;
@@ -1258,6 +1269,7 @@ __global__ void attn_tc_merge_kernel(const float* __restrict__ part_o, const flo
         acc.x += f * o.x; acc.y += f * o.y; acc.z += f * o.z; acc.w += f * o.w;
         l += f * part_ml[slot * 2 + 1];
     }
+    l += tl_sink_term(sink, head, m);
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     uint2 v;
     v.x = pack_bf16(acc.x * inv, acc.y * inv); v.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -1296,6 +1308,7 @@ static int tc2_prefill_impl(const void* q, int q_stride, void* out, const void* 
     if ((e = make_pages_map(&mk, k_pages, rows, page_size))) return e;
     if ((e = make_pages_map(&mv, v_pages, rows, page_size))) return e;
     TcAttnArgs A{};
+    A.sink = g_sink;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
@@ -1312,7 +1325,7 @@ static int tc2_prefill_impl(const void* q, int q_stride, void* out, const void* 
     constexpr int GROUPS = 256 / (D / 4);                  // (token, head) pairs a block of 256 threads
     const long long items = (long long)n_merge_rows * nq;
     attn_tc_merge_kernel<<<(unsigned)((items + GROUPS - 1) / GROUPS), 256, 0, stream>>>(part_o, part_ml, (bf16*)out, merge_rows, n_merge_rows,
-                                                                                       tokens, nq, A.ksplit);
+                                                                                       tokens, nq, A.ksplit, A.sink);
     return tl_launch_status();
 #else
     return 2;
@@ -1385,6 +1398,7 @@ TL_EXPORT int tl_attn_tc3_prefill(const void* q, int q_stride, void* out, const 
     if ((e = make_pages_map(&mk, k_pages, rows, page_size))) return e;
     if ((e = make_pages_map(&mv, v_pages, rows, page_size))) return e;
     TcAttnArgs A{};
+    A.sink = g_sink;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;

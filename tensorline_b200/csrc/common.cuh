@@ -69,6 +69,13 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// A softmax with a sink: the denominator of query head `head` holds one more term, exp(sink[head]), that has no key and
+// no value and is not scaled.  For kernels that keep (m, l) in base-2 units (l = sum of exp2(s - m)): the term to add to
+// l once, when the row is finished.  Null sink: nothing.  m = -inf (a row without keys) gives +inf, and the row comes out 0.
+__device__ __forceinline__ float tl_sink_term(const float* __restrict__ sink, int head, float m) {
+    return sink ? exp2f(fmaf(sink[head], 1.4426950408889634f, -m)) : 0.f;
+}
+
 static inline int tl_launch_status() { return (int)cudaGetLastError(); }
 
 // Host-side state that belongs to a device (kernel attributes that were set, addresses that were looked up) is

@@ -43,6 +43,8 @@ def attn_lib(head_dim: int):
         lib.tl_attn_decode_tma.restype = ctypes.c_int
         lib.tl_attn_decode_tma_rope.argtypes = lib.tl_attn_decode_tma.argtypes[:-1] + [_P, _P, _I, _I, _P]
         lib.tl_attn_decode_tma_rope.restype = ctypes.c_int
+        lib.tl_attn_set_sink.argtypes = [_P]
+        lib.tl_attn_set_sink.restype = ctypes.c_int
         if lib.tl_attn_decode_max_table() != DECODE_MAX_TABLE_ENTRIES:
             raise KernelError(f"the attention library copies {lib.tl_attn_decode_max_table()} block-table entries a block, "
                               f"the split planner assumes {DECODE_MAX_TABLE_ENTRIES}")
@@ -79,8 +81,18 @@ def attn_tc_lib(head_dim: int):
         lib.tl_attn_tc2p_prefill.restype = ctypes.c_int
         lib.tl_attn_tc2_prefill_split.argtypes = lib.tl_attn_tc2_prefill.argtypes[:-1] + [_I, _I, _I, _P, _P, _P, _I, _P]
         lib.tl_attn_tc2_prefill_split.restype = ctypes.c_int
+        lib.tl_attn_set_sink.argtypes = [_P]
+        lib.tl_attn_set_sink.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
+
+
+def _set_sink(lib, sink, nq: int) -> None:
+    """The sink of the library's launches that follow: float32 [nq] (one more term exp(sink[h]) in every softmax
+    denominator of query head h) or None.  Set before every launch."""
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nq or not sink.is_contiguous() or not sink.is_cuda):
+        raise KernelError("attention: sink must be a contiguous float32 device tensor with one entry a query head")
+    lib.tl_attn_set_sink(_ptr(sink))
 
 
 def tc_min_page(head_dim: int) -> int:
@@ -89,7 +101,7 @@ def tc_min_page(head_dim: int) -> int:
 
 
 def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-               nq, nkv, d, window, scale, order=None) -> None:
+               nq, nkv, d, window, scale, order=None, sink=None) -> None:
     """Prompt-portion attention on tcgen05: 128 query rows per block, S and O in tensor memory."""
     from .ops_gemm import status_word
     if page_size < tc_min_page(d) or page_size > KEY_TILE or page_size & (page_size - 1):
@@ -100,6 +112,7 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // TC_QUERY_TILE) for i in range(B))
     if order is not None:
         tiles = order.numel()                           # the array may leave requests out
+    _set_sink(attn_tc_lib(d), sink, nq)
     _check(attn_tc_lib(d).tl_attn_tc_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                              table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                              nq, nkv, int(window or 0), float(scale), tiles,
@@ -147,7 +160,7 @@ TC_P_IN_TMEM = {"0": False, "1": True}.get(os.environ.get("TENSORLINE_B200_TC_P_
 
 
 def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-                    nq, nkv, d, window, scale, order=None, p_in_tmem=None, ksplit: int = 1, merge_rows=None) -> bool:
+                    nq, nkv, d, window, scale, order=None, p_in_tmem=None, ksplit: int = 1, merge_rows=None, sink=None) -> bool:
     """Prompt-portion attention on tcgen05 with two query tiles (256 rows) per block and K, V by TMA.
     `p_in_tmem` (None: as the switch says): "64": P kept in tensor memory, key tiles of 64; False: P through shared
     memory; True: key tiles of 128 and P in tensor memory.  Head sizes 64 and 128, pages of 8 to 64 tokens; returns
@@ -165,6 +178,7 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
     if order is not None:
         tiles = order.numel()
     lib = attn_tc_lib(d)
+    _set_sink(lib, sink, nq)
     if ksplit > 1 and p_in_tmem is not True:
         T = out.shape[0]
         if merge_rows is None:
@@ -229,9 +243,10 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
 
 
 def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-            nq, nkv, d, window, scale, order=None) -> None:
+            nq, nkv, d, window, scale, order=None, sink=None) -> None:
     g = nq // nkv
     B = len(h_q_start) - 1
+    _set_sink(attn_lib(d), sink, nq)
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // KEY_TILE) for i in range(B))
     if order is not None:
         tiles = order.numel()
@@ -261,7 +276,7 @@ def decode_takes_rope(B: int, d: int, page_size: int) -> bool:
 
 def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, B,
            nq, nkv, d, window, scale, chunk, splits, part_o=None, part_ml=None, tma: bool | None = None,
-           cluster: bool | None = None, rope: dict | None = None) -> None:
+           cluster: bool | None = None, rope: dict | None = None, sink=None) -> None:
     """Split-KV decode attention.  `tma`: load K and V by TMA (head sizes that are multiples of 64, pages of
     8..64 tokens); None = wherever that applies.  `cluster` (TMA path, 2..8 key ranges, groups of at most 16
     heads): the ranges of a request merge inside a thread-block cluster, no partials, no second kernel;
@@ -271,6 +286,7 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
     runs the rotary kernel instead, for the case that the library turns the launch down."""
     if KEY_TILE % page_size:
         raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
+    _set_sink(attn_lib(d), sink, nq)
     use_tma = (TMA_DECODE and B >= TMA_DECODE_MIN_BATCH if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64
     if rope is not None and not use_tma:
         raise KernelError("attn_decode: the rotary step folds into the TMA kernel only")
@@ -315,8 +331,9 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                       _stream()), "attn_decode" + ("+combine" if splits > 1 else ""), launches=2 if splits > 1 else 1)
 
 
-def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale, rope: dict | None = None) -> None:
-    """`rope`: only for decode-only steps that `decode_takes_rope` accepted (see `decode`)."""
+def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale, rope: dict | None = None, sink=None) -> None:
+    """`rope`: only for decode-only steps that `decode_takes_rope` accepted (see `decode`).  `sink`: float32 [nq], one more
+    term exp(sink[h]) in the softmax denominators of head h (every kernel adds it once, where a row is finished)."""
     if qkv.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attend_bf16: bfloat16 tensors only")
     q_stride = qkv.shape[1]
@@ -332,7 +349,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
             part_o = torch.empty((ctx.B, nq, splits, d), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((ctx.B, nq, splits, 2), dtype=torch.float32, device=qkv.device)
         decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
-               ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, rope=rope)
+               ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, rope=rope, sink=sink)
     else:
         g = nq // nkv
         singles = _single_token_requests(ctx, qkv.device, g, nkv)
@@ -358,12 +375,12 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
                 with torch.cuda.stream(side):
                     side.wait_event(ready)
                     decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
-                           singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
+                           singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, sink=sink)
                     joined = torch.cuda.Event()
                     joined.record(side)
             else:
                 decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
-                       singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
+                       singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, sink=sink)
         rest = [i for i in range(ctx.B) if i not in skip]
         rest_rows = sum(ctx.h_q_start[i + 1] - ctx.h_q_start[i] for i in rest) * g
         # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05, and so do steps with a
@@ -402,16 +419,16 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
             if rows_key not in ctx.scratch:
                 rows = [t for i in rest for t in range(ctx.h_q_start[i], ctx.h_q_start[i + 1])]
                 ctx.scratch[rows_key] = torch.tensor(rows, dtype=torch.int32).to(qkv.device, non_blocking=True)
-            if not prefill_tc_pair(*args, order(2 * TC_QUERY_TILE), ksplit=ksplit, merge_rows=ctx.scratch[rows_key]):
+            if not prefill_tc_pair(*args, order(2 * TC_QUERY_TILE), ksplit=ksplit, merge_rows=ctx.scratch[rows_key], sink=sink):
                 ksplit = 1
         if ksplit >= 2:
             pass
-        elif use_tc and TC_PAIR and one_tile_blocks > ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
+        elif use_tc and TC_PAIR and one_tile_blocks > ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE), sink=sink):
             pass
         elif use_tc:
-            prefill_tc(*args, order(TC_QUERY_TILE))
+            prefill_tc(*args, order(TC_QUERY_TILE), sink=sink)
         else:
-            prefill(*args, order(KEY_TILE))
+            prefill(*args, order(KEY_TILE), sink=sink)
         if singles and joined is not None:
             torch.cuda.current_stream(qkv.device).wait_event(joined)
 

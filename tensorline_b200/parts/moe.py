@@ -8,7 +8,8 @@ The experts' matrices are stacked ([E, F, K] and [E, K, F]) at load time.  Steps
 (token, chosen expert) pair, that expert's rows (`ops.moe_up`, `ops.moe_down`): nothing is sorted and nothing comes
 back to the host, so the step sits in a CUDA graph.  Steps of many tokens sort the pairs by expert on the device,
 gather the tokens' rows in that order and run two dense products per expert on its run of rows (the engine's own
-products: the library for bfloat16, the exact-order kernel for float32), which needs the runs' bounds on the host.
+products), which needs the runs' bounds on the host.  The 32-bit engine streams always: a token's result is then the
+same chain of additions in every step, whatever else the step holds.
 """
 from __future__ import annotations
 
@@ -26,7 +27,7 @@ STREAM_MAX_TOKENS = int(os.environ.get("TENSORLINE_B200_MOE_STREAM_MAX_TOKENS", 
 
 @register_feed_forward("routed_experts")
 class RoutedExperts(Part):
-    graph_capturable = True              # steps of single tokens stay under STREAM_MAX_TOKENS rows... see forward
+    graph_capturable = True              # a captured step streams the experts whatever its size (see forward)
 
     def __init__(self, rt: Runtime, hidden: int, inner: int, experts: int, top: int, activation: str = "relu_squared",
                  router_bias: bool = True, names: dict | None = None):
@@ -67,7 +68,7 @@ class RoutedExperts(Part):
         wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
         ops.topk_softmax(z, top, idx, wts)
         y = torch.empty((T, self.hidden), dtype=h.dtype, device=h.device)
-        if T <= STREAM_MAX_TOKENS or ctx.graph_max_ctx:
+        if T <= STREAM_MAX_TOKENS or ctx.graph_max_ctx or self.rt.exact:
             a = torch.empty((T * top, self.inner), dtype=h.dtype, device=h.device)
             ops.moe_up(h, self.w_up, idx, a)
             ops.moe_down(a, self.w_down, idx, wts, y)

@@ -226,8 +226,9 @@ def test_sampling_matches_reference_distribution(top_p, V, R):
         assert lo - 1e-5 <= float(u[r]) <= float(cdf[got[r]]) + 1e-5, f"row {r}: u={float(u[r])} not in the token's interval"
 
 
-def _plain_attention_rows(q, k, v, pos_q, window):
-    """q [n, nq, d] at positions pos_q over the whole k, v [len, nkv, d]."""
+def _plain_attention_rows(q, k, v, pos_q, window, sink=None):
+    """q [n, nq, d] at positions pos_q over the whole k, v [len, nkv, d].  `sink` [nq]: the denominator of head h
+    also holds exp(sink[h])."""
     n, nq, d = q.shape
     g = nq // k.shape[1]
     out = torch.empty_like(q)
@@ -235,7 +236,11 @@ def _plain_attention_rows(q, k, v, pos_q, window):
         lo = max(0, p - window + 1) if window else 0
         for h in range(nq):
             s = (k[lo:p + 1, h // g] @ q[i, h]) * d ** -0.5
-            out[i, h] = torch.softmax(s, 0) @ v[lo:p + 1, h // g]
+            if sink is None:
+                out[i, h] = torch.softmax(s, 0) @ v[lo:p + 1, h // g]
+            else:
+                w = torch.softmax(torch.cat([s, sink[h:h + 1].to(s.dtype)]), 0)[:-1]
+                out[i, h] = w @ v[lo:p + 1, h // g]
     return out
 
 
@@ -262,10 +267,16 @@ ATT_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in th
 
 @pytest.mark.parametrize("case", ATT_CASES, ids=[f"q{c[0]}kv{c[1]}d{c[2]}p{c[3]}" for c in ATT_CASES])
 @pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16", "tcgen05_pair_split_bf16"])
-def test_paged_attention(case, kernel):
-    """Decode and prefill attention over scattered pages against the plain formula."""
+@pytest.mark.parametrize("with_sink", [False, True], ids=["", "sink"])
+def test_paged_attention(case, kernel, with_sink):
+    """Decode and prefill attention over scattered pages against the plain formula; with a sink, every head's
+    denominator holds one more term (heads with a large sink lose most of their weight to it, heads with a very
+    negative one nothing)."""
     from tensorline_b200 import ops, ops_attention
     nq, nkv, d, ps, ctx_lens, step_lens, window = case
+    sink_cpu = (rnd(nq, seed=7, scale=4.0) + 1.0) if with_sink else None
+    sink = sink_cpu.cuda() if with_sink else None
+    kw = {"sink": sink} if with_sink else {}
     if kernel in ("tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16", "tcgen05_pair_split_bf16") and d % 64:
         pytest.skip("no tcgen05 build for this head size")
     if kernel == "tcgen05_bf16" and (d % 64 or ps < 2):
@@ -297,7 +308,7 @@ def test_paged_attention(case, kernel):
             vps[mine[i // ps], :, i % ps] = v[i]
         rows.append(mine)
         pq = list(range(ctx_lens[b], n))
-        want.append(_plain_attention_rows(q.double(), k.double(), v.double(), pq, window))
+        want.append(_plain_attention_rows(q.double(), k.double(), v.double(), pq, window, sink_cpu))
         qs.append(q)
         pos_all += pq
         slot_all += [b] * step_lens[b]
@@ -317,7 +328,7 @@ def test_paged_attention(case, kernel):
         if kernel == "tcgen05_pair_split_bf16":             # every block's key tiles dealt out to three blocks (some get none)
             fn = functools.partial(ops_attention.prefill_tc_pair, p_in_tmem="64", ksplit=3)
         took = fn(q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
-                  q_start, nq, nkv, d, window, scale)
+                  q_start, nq, nkv, d, window, scale, **kw)
         from tensorline_b200 import ops_gemm
         ops_gemm.check_status()
         if kernel != "tcgen05_bf16":
@@ -330,11 +341,11 @@ def test_paged_attention(case, kernel):
         if order is not None:
             again = torch.zeros_like(out)
             fn(q_all, nq * d, again, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
-               q_start, nq, nkv, d, window, scale, order)
+               q_start, nq, nkv, d, window, scale, order, **kw)
             ops_gemm.check_status()
             assert torch.equal(again, out)
     elif kernel != "mma_bf16":
-        ops.attn_tokenwise(q_all, nq * d, out, kd, vd, table, ps, i32(pos_all), i32(slot_all), nq, nkv, d, window, scale)
+        ops.attn_tokenwise(q_all, nq * d, out, kd, vd, table, ps, i32(pos_all), i32(slot_all), nq, nkv, d, window, scale, **kw)
     else:
         q_start = [0]
         for n in step_lens:
@@ -354,14 +365,14 @@ def test_paged_attention(case, kernel):
                 # kernel or (2..8 ranges, groups of up to 16 heads) inside a thread-block cluster
                 for tma, cluster in ((False, False), (True, False), (True, True)):
                     out.zero_()
-                    ops_attention.decode(*args, B, nq, nkv, d, window, scale, chunk, splits, po, pml, tma=tma, cluster=cluster)
+                    ops_attention.decode(*args, B, nq, nkv, d, window, scale, chunk, splits, po, pml, tma=tma, cluster=cluster, **kw)
                     assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} splits, tma {tma}, cluster {cluster}", **BF16)
             out.zero_()
-        ops_attention.prefill(*args, q_start, nq, nkv, d, window, scale)
+        ops_attention.prefill(*args, q_start, nq, nkv, d, window, scale, **kw)
         order = ops_attention.tile_order(q_start, ctx_lens, nq // nkv, 64, "cuda")
         if order is not None:
             again = torch.zeros_like(out)
-            ops_attention.prefill(q_all, nq * d, again, *args[3:], q_start, nq, nkv, d, window, scale, order)
+            ops_attention.prefill(q_all, nq * d, again, *args[3:], q_start, nq, nkv, d, window, scale, order, **kw)
             assert torch.equal(again, out)
     assert_close(out.view(T, nq, d), torch.cat(want), kernel, **tol(adt))
 
