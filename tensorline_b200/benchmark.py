@@ -542,6 +542,84 @@ def run_ours(a):
     return 0
 
 
+# ------------------------------------------------------------------------------------------ another design beside Qwen2
+# `--design vutesun`: prefill and decode of the Vutesun decoder at sizes that resemble a real model's layers, beside the
+# Qwen2 decoder at equal size (same width, depth, attention heads and vocabulary; a dense feed-forward with as many
+# active weights a token as the routed one), random weights, with milliseconds per kernel class of one prompt step and
+# one eager decode step of each.
+DESIGN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, head=128, rec_heads=8, rec_dim=128, rec_vdim=256, ff=1024, experts=32, top=4,
+               vocab=32000, layers=4),
+    "4k": dict(width=4096, heads=32, kv_heads=8, head=128, rec_heads=16, rec_dim=128, rec_vdim=256, ff=1536, experts=16, top=2,
+               vocab=32000, layers=4),
+}
+
+
+def _vutesun_sizes(z):
+    moe = {"expert": {"ff": z["ff"]}, "kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}}
+    pair = {"type": "parallel", "mlp": moe, "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"], "scale": z["head"] ** -0.5,
+                 "rot": {"base": 500000.0, "dims": z["head"]}},
+        "right": {"heads": z["rec_heads"], "dim": z["rec_dim"], "vdim": z["rec_vdim"], "rot": {"base": 1e6, "dims": z["rec_dim"]},
+                  "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(1, z["rec_heads"] - 1)) for i in range(z["rec_heads"])]}}}
+    rec = {"type": "mlstm", "mlp": moe, "mixer": {"heads": z["rec_heads"], "dim": z["rec_dim"], "vdim": z["rec_vdim"], "gate_cap": 15.0}}
+    order = [pair, rec, rec, pair]
+    return {"architecture": "Vutesun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+            "layers": [order[i % 4] for i in range(z["layers"])]}
+
+
+def run_design(a):
+    import torch
+    from tensorline_b200 import Engine, Qwen2Config
+    from tensorline_b200.config.vutesun import VutesunConfig
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "ours", "error": "no CUDA device: this engine runs on the GPU only"}))
+        return 1
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    pk, pk_src = peaks()
+    context, batch, K, W = 2048 + 256, a.batch, a.steps, a.warmup
+    out = {}
+    for tag in (a.design_size.split(",") if a.design_size else sorted(DESIGN_SIZES)):
+        z = DESIGN_SIZES[tag]
+        dense = 2 * z["top"] * z["ff"] // 3 // 64 * 64                   # 3 H I = top * 2 H ff
+        arms = {"vutesun": VutesunConfig.from_dict(_vutesun_sizes(z)),
+                "qwen2": Qwen2Config.from_dict(dict(_sizes(z["layers"], z["width"], z["heads"], z["kv_heads"], dense, 1e-5),
+                                                    vocab_size=z["vocab"], eos_token_id=None))}
+        out[tag] = {"sizes": dict(z, dense_intermediate=dense)}
+        for name, cfg in arms.items():
+            weights = random_weights(cfg, device)
+            eng = Engine(cfg, dtype="bfloat16", weights=weights, block_size=PAGE, max_num_seqs=max(16, batch), max_batched_tokens=2048,
+                         max_model_len=context, num_blocks=max(16, batch) * (context // PAGE), prefix_caching=False, cuda_graphs=True)
+            del weights
+            V = cfg.vocab_size
+            ms_p = timed_prefill(eng, PREFILL_TOKENS, V, iters=12, warm=3)
+            ms_d, launches, _ = timed_decode(eng, batch, context - (K + W) - 1, K, W, V)
+            ms_1, _, _ = timed_decode(eng, 1, context - (K + W) - 1, K, W, V)
+            r = {"prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(ms_p, 3), "prefill_tok_s": round(1000 * PREFILL_TOKENS / ms_p),
+                 f"decode_b{batch}_ms": round(ms_d, 4), f"decode_b{batch}_tok_s": round(1000 * batch / ms_d, 1),
+                 "decode_b1_ms": round(ms_1, 4), "decode_b1_tok_s": round(1000 / ms_1, 1), "launches_per_decode_step": launches,
+                 "parameters": cfg.num_parameters()}
+            if a.profile:
+                r["profile"] = profile_steps(eng, V, batch, context - 8)
+            print(f"[bench] {tag} {name}: prefill {ms_p:.2f} ms ({r['prefill_tok_s']} tok/s), decode b{batch} {ms_d:.3f} ms, "
+                  f"b1 {ms_1:.3f} ms", file=sys.stderr, flush=True)
+            out[tag][name] = r
+            del eng
+            import gc
+            gc.collect(); torch.cuda.empty_cache()
+    first = out[sorted(out)[0]]
+    print(json.dumps({"metric": f"decode tok/s of the Vutesun decoder beside Qwen2 at equal layer sizes (bf16, batch {batch}, context {context})",
+                      "value": first["vutesun"][f"decode_b{batch}_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+                      "ms_per_step": first["vutesun"][f"decode_b{batch}_ms"], "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                      "config": {"model": "Vutesun and Qwen2 layer sizes of this file, random weights", "global_batch": batch,
+                                 "seq_len": context, "parallelism": "single GPU", "peaks": pk_src,
+                                 "l2": "inputs larger than L2 (weights, cache and state are re-read from HBM every step)"},
+                      "peaks": pk, "designs": out}))
+    return 0
+
+
 def run_reference(a):
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     try:
@@ -569,6 +647,9 @@ def main(argv=None):
     ap.add_argument("--timeline", action="store_true",
                     help="print the time line of one captured decode step from the kernels' own stamps (needs TENSORLINE_B200_TRACE=1)")
     ap.add_argument("--no-warm-mix", dest="warm_mix", action="store_false", help="mix: time the first pass (graph capture included)")
+    ap.add_argument("--design", choices=["vutesun"], default=None,
+                    help="instead of the default workload: this design beside Qwen2 at equal layer sizes (prefill, decode, --profile)")
+    ap.add_argument("--design-size", default="", help="--design: which of the sizes (2k, 4k; commas between them; default all)")
     a = ap.parse_args(argv)
     if a.warmup < 3:
         a.warmup = 3
@@ -577,4 +658,6 @@ def main(argv=None):
         return 2
     if a.impl == "reference":
         return run_reference(a)
+    if a.design:
+        return run_design(a)
     return run_ours(a)

@@ -8,7 +8,8 @@
 // expert's rows (moe_up), and every token sums its experts' down products in the order they were chosen (moe_down):
 // one pass over the weights the step needs, no sorting, nothing on the host, so the step can sit in a CUDA graph.
 // Steps of many tokens: the pairs are sorted by expert on the device (moe_sort), the tokens' rows gathered in that
-// order, every expert runs two dense products on its run of rows, and moe_combine sums each token's rows by weight.
+// order (every expert's run in a buffer of `cap` rows of its own, so that one batched product serves all experts), two
+// dense products run on them, and moe_combine sums each token's rows by weight.
 // Every output element is one fixed chain of additions, so a token's result does not depend on the step's other tokens.
 #include "common.cuh"
 
@@ -35,6 +36,44 @@ template <> __device__ __forceinline__ float warp_dot<bf16>(const bf16* __restri
         for (int k = lane; k < K; k += 32) acc = fmaf(__bfloat162float(w[k]), x[k], acc);
     }
     return warp_sum(acc);
+}
+
+// Four rows (`rows` of them real, a row `ld` elements after the other) against the same vector: the loads of all four are
+// issued before the first product, so a warp keeps four times as many bytes in flight.  A row's sum is the chain of
+// warp_dot, whichever rows share the call.
+template <typename TW> __device__ __forceinline__ void warp_dot4(const TW* __restrict__ w, int ld, int rows, const float* __restrict__ x,
+                                                                 int K, int lane, float (&out)[4]);
+template <> __device__ __forceinline__ void warp_dot4<float>(const float* __restrict__ w, int ld, int rows, const float* __restrict__ x,
+                                                             int K, int lane, float (&out)[4]) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) out[r] = r < rows ? warp_dot<float>(w + (size_t)r * ld, x, K, lane) : 0.f;
+}
+template <> __device__ __forceinline__ void warp_dot4<bf16>(const bf16* __restrict__ w, int ld, int rows, const float* __restrict__ x,
+                                                            int K, int lane, float (&out)[4]) {
+    if ((K & 7) || (ld & 7) || (((uintptr_t)w) & 15)) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) out[r] = r < rows ? warp_dot<bf16>(w + (size_t)r * ld, x, K, lane) : 0.f;
+        return;
+    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = lane * 8; k < K; k += 256) {
+        uint4 v[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) v[r] = r < rows ? *reinterpret_cast<const uint4*>(w + (size_t)r * ld + k) : make_uint4(0, 0, 0, 0);
+        const float4 x0 = *reinterpret_cast<const float4*>(x + k), x1 = *reinterpret_cast<const float4*>(x + k + 4);
+        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[r]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[r] = fmaf(__low2float(p[e]), xv[2 * e], acc[r]);
+                acc[r] = fmaf(__high2float(p[e]), xv[2 * e + 1], acc[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) out[r] = warp_sum(acc[r]);
 }
 
 // ------------------------------------------------------------------ small projection in float
@@ -117,10 +156,13 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * K + k]);
     __syncthreads();
     const TW* w = w_up + (size_t)e * F * K;
-    const int f0 = blockIdx.y * MOE_ROWS;
-    for (int f = f0 + wid; f < min(F, f0 + MOE_ROWS); f += 4) {
-        const float u = fmaxf(warp_dot<TW>(w + (size_t)f * K, xs, K, lane), 0.f);
-        if (lane == 0) a[(size_t)pair * F + f] = from_f<TA>(u * u);
+    const int f0 = blockIdx.y * MOE_ROWS + wid * (MOE_ROWS / 4), f1 = min(F, f0 + MOE_ROWS / 4);    // a warp's eight rows
+    for (int f = f0; f < f1; f += 4) {                   // four rows at a time: their loads are in flight together
+        float u[4];
+        warp_dot4<TW>(w + (size_t)f * K, K, min(4, f1 - f), xs, K, lane, u);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (lane == 0 && f + r < f1) { const float v = fmaxf(u[r], 0.f); a[(size_t)pair * F + f + r] = from_f<TA>(v * v); }
     }
 }
 
@@ -132,15 +174,20 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a,
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     for (int k = threadIdx.x; k < top * F; k += blockDim.x) xs[k] = to_f<TA>(a[(size_t)t * top * F + k]);
     __syncthreads();
-    const int n0 = blockIdx.y * MOE_ROWS;
-    for (int n = n0 + wid; n < min(N, n0 + MOE_ROWS); n += 4) {
-        float acc = 0.f;
+    const int n0 = blockIdx.y * MOE_ROWS + wid * (MOE_ROWS / 4), n1 = min(N, n0 + MOE_ROWS / 4);    // a warp's eight rows
+    for (int n = n0; n < n1; n += 4) {                   // four rows of one expert at a time, the experts in the order chosen
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int j = 0; j < top; ++j) {
             const int e = idx[(size_t)t * top + j];
-            const float v = warp_dot<TW>(w_down + ((size_t)e * N + n) * F, xs + (size_t)j * F, F, lane);
-            acc = fmaf(wts[(size_t)t * top + j], v, acc);
+            float v[4];
+            warp_dot4<TW>(w_down + ((size_t)e * N + n) * F, F, min(4, n1 - n), xs + (size_t)j * F, F, lane, v);
+            const float wj = wts[(size_t)t * top + j];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[r] = fmaf(wj, v[r], acc[r]);
         }
-        if (lane == 0) y[(size_t)t * N + n] = from_f<TA>(acc);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (lane == 0 && n + r < n1) y[(size_t)t * N + n + r] = from_f<TA>(acc[r]);
     }
 }
 
@@ -224,17 +271,27 @@ TL_EXPORT int tl_moe_sort(const int* idx, int P, int E, int* offsets, int* place
     return tl_launch_status();
 }
 
-// rows[place, :] = h[pair_at[place] / top, :]
+// Where a sorted place lies in the experts' row buffer.  cap = 0: the runs lie one behind the other (row = place);
+// cap > 0: every expert has `cap` rows of its own (row = expert * cap + place - offsets[expert]), so that one batched
+// product serves all experts; rows beyond an expert's run stay as the caller filled them.
+__device__ __forceinline__ size_t moe_row(int place, int expert, const int* __restrict__ offsets, int cap) {
+    return cap ? (size_t)expert * cap + (place - offsets[expert]) : (size_t)place;
+}
+
+// rows[row of place, :] = h[pair_at[place] / top, :]
 template <typename TA>
-__global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restrict__ pair_at, TA* __restrict__ rows, int K, int top) {
-    const size_t src = (size_t)(pair_at[blockIdx.x] / top) * K, dst = (size_t)blockIdx.x * K;
+__global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restrict__ pair_at, const int* __restrict__ idx,
+                                  const int* __restrict__ offsets, int cap, TA* __restrict__ rows, int K, int top) {
+    const int pair = pair_at[blockIdx.x];
+    const size_t src = (size_t)(pair / top) * K, dst = moe_row(blockIdx.x, idx[pair], offsets, cap) * K;
     for (int k = threadIdx.x; k < K; k += blockDim.x) rows[dst + k] = h[src + k];
 }
 
-TL_EXPORT int tl_moe_gather(const void* h, int act_dtype, const int* pair_at, void* rows, int P, int K, int top, cudaStream_t stream) {
+TL_EXPORT int tl_moe_gather(const void* h, int act_dtype, const int* pair_at, const int* idx, const int* offsets, int cap,
+                            void* rows, int P, int K, int top, cudaStream_t stream) {
     if (P <= 0) return 0;
-    if (act_dtype == TL_F32) moe_gather_kernel<float><<<P, 256, 0, stream>>>((const float*)h, pair_at, (float*)rows, K, top);
-    else moe_gather_kernel<bf16><<<P, 256, 0, stream>>>((const bf16*)h, pair_at, (bf16*)rows, K, top);
+    if (act_dtype == TL_F32) moe_gather_kernel<float><<<P, 256, 0, stream>>>((const float*)h, pair_at, idx, offsets, cap, (float*)rows, K, top);
+    else moe_gather_kernel<bf16><<<P, 256, 0, stream>>>((const bf16*)h, pair_at, idx, offsets, cap, (bf16*)rows, K, top);
     return tl_launch_status();
 }
 
@@ -255,23 +312,26 @@ TL_EXPORT int tl_relu_square(void* u, int act_dtype, long long n, cudaStream_t s
     return tl_launch_status();
 }
 
-// y[t, :] = sum_j wts[t, j] * rows[place_of[t * top + j], :], j in the order chosen
+// y[t, :] = sum_j wts[t, j] * rows[row of place_of[t * top + j], :], j in the order chosen
 template <typename TA>
-__global__ void moe_combine_kernel(const TA* __restrict__ rows, const int* __restrict__ place_of, const float* __restrict__ wts,
+__global__ void moe_combine_kernel(const TA* __restrict__ rows, const int* __restrict__ place_of, const int* __restrict__ idx,
+                                   const int* __restrict__ offsets, int cap, const float* __restrict__ wts,
                                    TA* __restrict__ y, int N, int top) {
     const int t = blockIdx.x;
     for (int n = threadIdx.x; n < N; n += blockDim.x) {
         float acc = 0.f;
-        for (int j = 0; j < top; ++j)
-            acc = fmaf(wts[(size_t)t * top + j], to_f<TA>(rows[(size_t)place_of[(size_t)t * top + j] * N + n]), acc);
+        for (int j = 0; j < top; ++j) {
+            const size_t pair = (size_t)t * top + j;
+            acc = fmaf(wts[pair], to_f<TA>(rows[moe_row(place_of[pair], idx[pair], offsets, cap) * N + n]), acc);
+        }
         y[(size_t)t * N + n] = from_f<TA>(acc);
     }
 }
 
-TL_EXPORT int tl_moe_combine(const void* rows, int act_dtype, const int* place_of, const float* wts, void* y, int T, int N,
-                             int top, cudaStream_t stream) {
+TL_EXPORT int tl_moe_combine(const void* rows, int act_dtype, const int* place_of, const int* idx, const int* offsets, int cap,
+                             const float* wts, void* y, int T, int N, int top, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (act_dtype == TL_F32) moe_combine_kernel<float><<<T, 256, 0, stream>>>((const float*)rows, place_of, wts, (float*)y, N, top);
-    else moe_combine_kernel<bf16><<<T, 256, 0, stream>>>((const bf16*)rows, place_of, wts, (bf16*)y, N, top);
+    if (act_dtype == TL_F32) moe_combine_kernel<float><<<T, 256, 0, stream>>>((const float*)rows, place_of, idx, offsets, cap, wts, (float*)y, N, top);
+    else moe_combine_kernel<bf16><<<T, 256, 0, stream>>>((const bf16*)rows, place_of, idx, offsets, cap, wts, (bf16*)y, N, top);
     return tl_launch_status();
 }

@@ -15,18 +15,17 @@
 // activation type, as the projection left them.
 //
 // Work split.  grid (requests, heads, value-column slices of SCAN_JS): a block walks its request's tokens of the
-// step in order, SCAN_C at a time.  A thread owns one value column and every SCAN_IS-th row of S in registers
-// (R rows), so a token costs it R updates and R products and no synchronisation; the column sums are finished by
-// shuffles over the SCAN_IS lanes that share a column.  The sequence of operations on a state element and on an
+// step in order, SCAN_C at a time.  A thread owns one value column and R consecutive rows of S in registers (IS
+// threads a column, R * IS >= d), so a token costs it R updates and R products and no synchronisation; the column
+// sums are finished by shuffles over the IS lanes that share a column.  The sequence of operations on a state element and on an
 // output is the same wherever the step was cut, so portions, single tokens and whole prompts give the same bits.
 // The state lies in memory as the threads hold it ([row group][thread]; loads and stores of a step of single
 // tokens, which are all that step moves, are contiguous); the gated kind keeps m, and each column slice its own
 // copy of n and m, behind it.  Nobody else reads the state.
 #include "common.cuh"
 
-constexpr int SCAN_IS = 8;
-constexpr int SCAN_JS = 16;
-constexpr int SCAN_C = 16;
+constexpr int SCAN_JS = 16;      // value columns a block
+constexpr int SCAN_C = 16;       // tokens a chunk
 
 struct ScanArgs {
     const void* proj; int stride;          // the step's projection rows [T, stride]
@@ -44,28 +43,34 @@ struct ScanArgs {
     float den_eps;
 };
 
-template <bool GATED> struct ScanShape {
+// A head's d rows are dealt out to IS threads a column, R consecutive rows each (R * IS >= d; the rows beyond d are zeros).
+template <int R, int IS, bool GATED> struct ScanShape {
     static constexpr int JW = SCAN_JS + (GATED ? 1 : 0);
-    static constexpr int NT = (SCAN_IS * JW + 31) / 32 * 32;
+    static constexpr int NT = (IS * JW + 31) / 32 * 32;
+    static constexpr int PB = R * NT + (GATED ? 4 : 0);          // floats of state a (head, column slice)
+    static constexpr int RS = R + 4;                             // a thread's rows of q or k in shared memory, padded: the
+    static constexpr int TS = IS * RS;                           // 16-byte reads of the IS threads of a column hit different banks
 };
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename TA, int R, bool GATED>
-__global__ void __launch_bounds__(ScanShape<GATED>::NT) linear_scan_kernel(const ScanArgs A) {
-    constexpr int JW = ScanShape<GATED>::JW, NT = ScanShape<GATED>::NT;
-    constexpr int PB = R * NT + (GATED ? 4 : 0);
-    extern __shared__ float sm[];
+template <typename TA, int R, int IS, bool GATED>
+__global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_scan_kernel(const ScanArgs A) {
+    using Sh = ScanShape<R, IS, GATED>;
+    constexpr int NT = Sh::NT, PB = Sh::PB, RS = Sh::RS, TS = Sh::TS;
+    constexpr int PF = (SCAN_C * R * IS + NT - 1) / NT;           // q (and k) elements of a chunk a thread fetches
+    constexpr int PV = (SCAN_C * SCAN_JS + NT - 1) / NT;          // v elements
+    extern __shared__ __align__(16) float sm[];
     const int d = A.d;
-    float* qs = sm;
-    float* ks = qs + SCAN_C * d;
-    float* vs = ks + SCAN_C * d;
+    float* qs = sm;                                                // [C][IS][RS]
+    float* ks = qs + SCAN_C * TS;
+    float* vs = ks + SCAN_C * TS;                                  // [C][JS]
     float* ga = vs + SCAN_C * SCAN_JS;
     float* gb = ga + SCAN_C;
     float* gm = gb + SCAN_C;
     float* nq = gm + SCAN_C;
     const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
-    const int tid = threadIdx.x, islice = tid % SCAN_IS, j = tid / SCAN_IS;
+    const int tid = threadIdx.x, islice = tid % IS, j = tid / IS;
     const int t0 = A.q_start[b], t1 = A.q_start[b + 1];
     float* st = A.state + (size_t)A.slots[b] * A.slot_stride + ((size_t)h * gridDim.z + z) * PB;
     float S[R];
@@ -78,38 +83,72 @@ __global__ void __launch_bounds__(ScanShape<GATED>::NT) linear_scan_kernel(const
     const float dec = GATED ? 0.f : A.decay[h];
     const TA* proj = (const TA*)A.proj;
     const int rhalf = A.rot >> 1;
+    for (int i = tid; i < 2 * SCAN_C * TS; i += NT) sm[i] = 0.f;   // rows beyond d and the padding stay zero
+
+    // The next chunk's q, k, v (as the projection left them) and gate pre-activations wait in registers while this
+    // chunk is worked through: their loads are issued before the chunk's arithmetic and used after it.
+    float fq[PF], fk[PF], fv[PV], fgi = 0.f, fgf = 0.f;
+    auto fetch = [&](int c0) {
+        const int n = min(SCAN_C, t1 - c0);
+#pragma unroll
+        for (int it = 0; it < PF; ++it) {
+            const int idx = tid + it * NT, t = idx / d, e = idx - t * d;
+            fq[it] = fk[it] = 0.f;
+            if (t < n) {
+                const TA* row = proj + (size_t)(c0 + t) * A.stride + (size_t)h * d + e;
+                fq[it] = to_f<TA>(row[A.q_off]);
+                fk[it] = to_f<TA>(row[A.k_off]);
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < PV; ++it) {
+            const int idx = tid + it * NT, t = idx / SCAN_JS, col = z * SCAN_JS + (idx - t * SCAN_JS);
+            fv[it] = (t < n && col < A.dv) ? to_f<TA>(proj[(size_t)(c0 + t) * A.stride + A.v_off + (size_t)h * A.dv + col]) : 0.f;
+        }
+        if (GATED && tid < n) {
+            const float* g = A.gates + (size_t)(c0 + tid) * 2 * A.H;
+            fgi = g[h]; fgf = g[A.H + h];
+        }
+    };
+    // element e of token t of the chunk in qs / ks
+    auto at = [&](int t, int e) { return t * TS + (e / R) * RS + (e % R); };
+    if (t0 < t1) fetch(t0);
+    __syncthreads();
 
     for (int c0 = t0; c0 < t1; c0 += SCAN_C) {
         const int n = min(SCAN_C, t1 - c0);
-        // q and k of the chunk: rotation by position, then the scale
-        for (int idx = tid; idx < n * d; idx += NT) {
-            const int t = idx / d, e = idx - t * d;
-            const TA* row = proj + (size_t)(c0 + t) * A.stride + (size_t)h * d;
-            float qv = to_f<TA>(row[A.q_off + e]), kv = to_f<TA>(row[A.k_off + e]);
-            if (e < A.rot) {
-                int i, partner; float sign;
-                if (A.interleaved) { i = e >> 1; partner = e ^ 1; sign = (e & 1) ? 1.f : -1.f; }
-                else { i = e < rhalf ? e : e - rhalf; partner = e < rhalf ? e + rhalf : e - rhalf; sign = e < rhalf ? -1.f : 1.f; }
-                float s, c;
-                sincosf(__fmul_rn((float)A.pos[c0 + t], A.inv_freq[i]), &s, &c);
-                const float qp = to_f<TA>(row[A.q_off + partner]), kp = to_f<TA>(row[A.k_off + partner]);
-                qv = __fmul_rn(qv, c) + sign * __fmul_rn(qp, s);
-                kv = __fmul_rn(kv, c) + sign * __fmul_rn(kp, s);
+        // the chunk into shared memory; dimensions that are not rotated get their scale here
+#pragma unroll
+        for (int it = 0; it < PF; ++it) {
+            const int idx = tid + it * NT, t = idx / d, e = idx - t * d;
+            if (t < n) {
+                qs[at(t, e)] = e < A.rot ? fq[it] : fq[it] * A.q_scale;
+                ks[at(t, e)] = e < A.rot ? fk[it] : fk[it] * A.k_scale;
             }
-            qs[t * d + e] = qv * A.q_scale;
-            ks[t * d + e] = kv * A.k_scale;
         }
-        for (int idx = tid; idx < n * SCAN_JS; idx += NT) {
-            const int t = idx / SCAN_JS, jj = idx - t * SCAN_JS, col = z * SCAN_JS + jj;
-            vs[idx] = col < A.dv ? to_f<TA>(proj[(size_t)(c0 + t) * A.stride + A.v_off + (size_t)h * A.dv + col]) : 0.f;
+#pragma unroll
+        for (int it = 0; it < PV; ++it) {
+            const int idx = tid + it * NT;
+            if (idx < n * SCAN_JS) vs[idx] = fv[it];
+        }
+        if (GATED && tid < n) {
+            gb[tid] = A.cap * tanhf(fgi / A.cap);
+            ga[tid] = log_sigmoid(A.cap * tanhf(fgf / A.cap));
+        }
+        __syncthreads();
+        // rotation by position, a pair of dimensions a thread, then the scale
+        for (int p = tid; p < n * rhalf; p += NT) {
+            const int t = p / rhalf, i = p - t * rhalf;
+            const int e1 = at(t, A.interleaved ? 2 * i : i), e2 = at(t, A.interleaved ? 2 * i + 1 : i + rhalf);
+            float sn, cs;
+            sincosf(__fmul_rn((float)A.pos[c0 + t], A.inv_freq[i]), &sn, &cs);
+            const float q1 = qs[e1], q2 = qs[e2], k1 = ks[e1], k2 = ks[e2];
+            qs[e1] = (__fmul_rn(q1, cs) - __fmul_rn(q2, sn)) * A.q_scale;
+            qs[e2] = (__fmul_rn(q2, cs) + __fmul_rn(q1, sn)) * A.q_scale;
+            ks[e1] = (__fmul_rn(k1, cs) - __fmul_rn(k2, sn)) * A.k_scale;
+            ks[e2] = (__fmul_rn(k2, cs) + __fmul_rn(k1, sn)) * A.k_scale;
         }
         if (GATED) {
-            if (tid < n) {
-                const float* g = A.gates + (size_t)(c0 + tid) * 2 * A.H;
-                gb[tid] = A.cap * tanhf(g[h] / A.cap);
-                ga[tid] = log_sigmoid(A.cap * tanhf(g[A.H + h] / A.cap));
-            }
-            __syncthreads();
             if (tid == 0) {                              // the running maximum is the only serial part
                 float m = m_run;
                 for (int t = 0; t < n; ++t) { m = fmaxf(ga[t] + m, gb[t]); gm[t] = m; }
@@ -126,8 +165,11 @@ __global__ void __launch_bounds__(ScanShape<GATED>::NT) linear_scan_kernel(const
         }
         __syncthreads();
         if (GATED) m_run = gm[n - 1];
+        if (c0 + SCAN_C < t1) fetch(c0 + SCAN_C);
 
         float po[SCAN_C];
+        const float* kt = ks + islice * RS;
+        const float* qt = qs + islice * RS;
 #pragma unroll
         for (int t = 0; t < SCAN_C; ++t) {
             po[t] = 0.f;
@@ -137,21 +179,21 @@ __global__ void __launch_bounds__(ScanShape<GATED>::NT) linear_scan_kernel(const
                 const float bv = GATED ? gb[t] * v : v;
                 float acc = 0.f;
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = r * SCAN_IS + islice;
-                    if (i < d) {
-                        S[r] = fmaf(a, S[r], ks[t * d + i] * bv);
-                        acc = fmaf(S[r], qs[t * d + i], acc);
-                    }
+                for (int r = 0; r < R; r += 4) {
+                    const float4 kk = *reinterpret_cast<const float4*>(kt + t * TS + r);
+                    const float4 qq = *reinterpret_cast<const float4*>(qt + t * TS + r);
+                    S[r] = fmaf(a, S[r], kk.x * bv);         acc = fmaf(S[r], qq.x, acc);
+                    S[r + 1] = fmaf(a, S[r + 1], kk.y * bv); acc = fmaf(S[r + 1], qq.y, acc);
+                    S[r + 2] = fmaf(a, S[r + 2], kk.z * bv); acc = fmaf(S[r + 2], qq.z, acc);
+                    S[r + 3] = fmaf(a, S[r + 3], kk.w * bv); acc = fmaf(S[r + 3], qq.w, acc);
                 }
                 po[t] = acc;
             }
         }
 #pragma unroll
         for (int t = 0; t < SCAN_C; ++t) {
-            po[t] += __shfl_xor_sync(0xffffffffu, po[t], 1);
-            po[t] += __shfl_xor_sync(0xffffffffu, po[t], 2);
-            po[t] += __shfl_xor_sync(0xffffffffu, po[t], 4);
+#pragma unroll
+            for (int o = 1; o < IS; o <<= 1) po[t] += __shfl_xor_sync(0xffffffffu, po[t], o);
         }
         if (GATED) {
             if (ones && islice == 0) {
@@ -177,29 +219,49 @@ __global__ void __launch_bounds__(ScanShape<GATED>::NT) linear_scan_kernel(const
     if (GATED && tid == 0) st[R * NT] = m_run;
 }
 
-// Floats of state per (head, column slice) for a head of d rows; 0: d is too large.
-static int scan_rows(int d) { return d <= 32 ? 4 : d <= 64 ? 8 : d <= 128 ? 16 : d <= 256 ? 32 : 0; }
+// How a head of d rows is dealt out: 0: R 4 x IS 8 (d <= 32), 1: 8 x 8 (<= 64), 2: 8 x 16 (<= 128), 3: 8 x 32 (<= 256); -1: too large.
+static int scan_shape(int d) { return d <= 32 ? 0 : d <= 64 ? 1 : d <= 128 ? 2 : d <= 256 ? 3 : -1; }
 
+// Floats of state per (head, column slice) for a head of d rows; 0: d is too large.
 TL_EXPORT int tl_scan_state_floats(int d, int gated) {
-    const int R = scan_rows(d);
-    if (!R) return 0;
-    return gated ? R * ScanShape<true>::NT + 4 : R * ScanShape<false>::NT;
+    switch (scan_shape(d)) {
+        case 0: return gated ? ScanShape<4, 8, true>::PB : ScanShape<4, 8, false>::PB;
+        case 1: return gated ? ScanShape<8, 8, true>::PB : ScanShape<8, 8, false>::PB;
+        case 2: return gated ? ScanShape<8, 16, true>::PB : ScanShape<8, 16, false>::PB;
+        case 3: return gated ? ScanShape<8, 32, true>::PB : ScanShape<8, 32, false>::PB;
+    }
+    return 0;
 }
 TL_EXPORT int tl_scan_columns() { return SCAN_JS; }
 
+template <typename TA, int R, int IS, bool GATED>
+static int launch_scan_shape(const ScanArgs& A, int B, cudaStream_t stream) {
+    using Sh = ScanShape<R, IS, GATED>;
+    const int nz = (A.dv + SCAN_JS - 1) / SCAN_JS;
+    const size_t smem = (size_t)(2 * SCAN_C * Sh::TS + SCAN_C * SCAN_JS + 4 * SCAN_C) * sizeof(float);
+    if (smem > 48 * 1024) {                              // the widest heads: more dynamic shared memory than a kernel has by default
+        static bool raised[TL_MAX_DEVICES] = {};
+        const int dev = tl_device_index();
+        if (dev < 0) return 1;
+        if (!raised[dev]) {
+            const cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<TA, R, IS, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            raised[dev] = true;
+        }
+    }
+    linear_scan_kernel<TA, R, IS, GATED><<<dim3(B, A.H, nz), Sh::NT, smem, stream>>>(A);
+    return tl_launch_status();
+}
+
 template <typename TA, bool GATED>
 static int launch_scan(const ScanArgs& A, int B, cudaStream_t stream) {
-    const int nz = (A.dv + SCAN_JS - 1) / SCAN_JS;
-    const dim3 grid(B, A.H, nz), block(ScanShape<GATED>::NT);
-    const size_t smem = (size_t)(2 * SCAN_C * A.d + SCAN_C * SCAN_JS + 4 * SCAN_C) * sizeof(float);
-    switch (scan_rows(A.d)) {
-        case 4: linear_scan_kernel<TA, 4, GATED><<<grid, block, smem, stream>>>(A); break;
-        case 8: linear_scan_kernel<TA, 8, GATED><<<grid, block, smem, stream>>>(A); break;
-        case 16: linear_scan_kernel<TA, 16, GATED><<<grid, block, smem, stream>>>(A); break;
-        case 32: linear_scan_kernel<TA, 32, GATED><<<grid, block, smem, stream>>>(A); break;
-        default: return 1;
+    switch (scan_shape(A.d)) {
+        case 0: return launch_scan_shape<TA, 4, 8, GATED>(A, B, stream);
+        case 1: return launch_scan_shape<TA, 8, 8, GATED>(A, B, stream);
+        case 2: return launch_scan_shape<TA, 8, 16, GATED>(A, B, stream);
+        case 3: return launch_scan_shape<TA, 8, 32, GATED>(A, B, stream);
     }
-    return tl_launch_status();
+    return 1;
 }
 
 TL_EXPORT int tl_linear_scan(const void* proj, int act_dtype, int stride, int q_off, int k_off, int v_off,
@@ -208,7 +270,7 @@ TL_EXPORT int tl_linear_scan(const void* proj, int act_dtype, int stride, int q_
                              long long slot_stride, const int* q_start, const int* slots, float* out, int B, int H,
                              int d, int dv, float den_eps, cudaStream_t stream) {
     if (B <= 0 || H <= 0) return 0;
-    if (B > 65535 * 32768 || H > 65535 || (rot & 1) || rot > d) return 1;
+    if (H > 65535 || (rot & 1) || rot > d) return 1;
     const ScanArgs A{proj, stride, q_off, k_off, v_off, gates, cap, decay, inv_freq, rot, interleaved, pos, q_scale, k_scale,
                      state, slot_stride, q_start, slots, out, H, d, dv, den_eps};
     const bool gated = gates != nullptr;

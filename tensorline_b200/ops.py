@@ -38,9 +38,9 @@ _SIGNATURES = {
     "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "tl_moe_sort": [_P, _I, _I, _P, _P, _P, _P],
-    "tl_moe_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P],
     "tl_relu_square": [_P, _I, ctypes.c_longlong, _P],
-    "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
+    "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
 }
 
 
@@ -562,13 +562,18 @@ def moe_sort(idx: torch.Tensor, E: int):
     return offsets, place_of, pair_at
 
 
-def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, top: int, rows: torch.Tensor) -> None:
-    """rows[place] = h[pair_at[place] // top]."""
-    P, K = rows.shape
-    if h.shape[1] != K or rows.dtype != h.dtype or pair_at.numel() != P:
-        raise KernelError("moe_gather: rows [P, K] of h's type")
-    _contig(h, "h"); _contig(rows, "rows"); _ints(pair_at, "pair_at")
-    _check(core().tl_moe_gather(_ptr(h), dtype_code(h.dtype), _ptr(pair_at), _ptr(rows), P, K, int(top), _stream()), "moe_gather")
+def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, idx: torch.Tensor, offsets: torch.Tensor, top: int, rows: torch.Tensor,
+               cap: int = 0) -> None:
+    """rows[row of place] = h[pair_at[place] // top].  cap 0: row = place (rows [P, K], the experts' runs one behind the
+    other); cap > 0: every expert has cap rows of its own (rows [E * cap, K], row = expert * cap + place - offsets[expert];
+    the rows behind a run are left as they are)."""
+    P, K = pair_at.numel(), rows.shape[1]
+    E = offsets.numel() - 1
+    if h.shape[1] != K or rows.dtype != h.dtype or rows.shape[0] != (E * cap if cap else P) or idx.numel() != P:
+        raise KernelError("moe_gather: rows [P, K] (or [E cap, K]) of h's type")
+    _contig(h, "h"); _contig(rows, "rows"); _ints(pair_at, "pair_at"); _ints(idx, "idx"); _ints(offsets, "offsets")
+    _check(core().tl_moe_gather(_ptr(h), dtype_code(h.dtype), _ptr(pair_at), _ptr(idx), _ptr(offsets), int(cap), _ptr(rows), P, K,
+                                int(top), _stream()), "moe_gather")
 
 
 def relu_square(u: torch.Tensor) -> None:
@@ -577,12 +582,14 @@ def relu_square(u: torch.Tensor) -> None:
     _check(core().tl_relu_square(_ptr(u), dtype_code(u.dtype), u.numel(), _stream()), "relu_square")
 
 
-def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, wts: torch.Tensor, y: torch.Tensor) -> None:
-    """y[t] = sum_j wts[t, j] * rows[place_of[t * top + j]]."""
+def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, idx: torch.Tensor, offsets: torch.Tensor, wts: torch.Tensor,
+                y: torch.Tensor, cap: int = 0) -> None:
+    """y[t] = sum_j wts[t, j] * rows[row of place_of[t * top + j]]; rows laid out as `moe_gather` lays them out."""
     T, top = wts.shape
     N = y.shape[1]
-    if rows.shape != (T * top, N) or rows.dtype != y.dtype or y.shape[0] != T or wts.dtype != torch.float32:
-        raise KernelError("moe_combine: rows [T top, N] of y's type, wts float32 [T, top]")
-    _contig(rows, "rows"); _ints(place_of, "place_of"); _contig(wts, "wts"); _contig(y, "y")
-    _check(core().tl_moe_combine(_ptr(rows), dtype_code(rows.dtype), _ptr(place_of), _ptr(wts), _ptr(y), T, N, top, _stream()),
-           "moe_combine")
+    E = offsets.numel() - 1
+    if rows.shape != ((E * cap if cap else T * top), N) or rows.dtype != y.dtype or y.shape[0] != T or wts.dtype != torch.float32:
+        raise KernelError("moe_combine: rows [T top, N] (or [E cap, N]) of y's type, wts float32 [T, top]")
+    _contig(rows, "rows"); _ints(place_of, "place_of"); _ints(idx, "idx"); _ints(offsets, "offsets"); _contig(wts, "wts"); _contig(y, "y")
+    _check(core().tl_moe_combine(_ptr(rows), dtype_code(rows.dtype), _ptr(place_of), _ptr(idx), _ptr(offsets), int(cap), _ptr(wts),
+                                 _ptr(y), T, N, top, _stream()), "moe_combine")

@@ -7,8 +7,9 @@
 The experts' matrices are stacked ([E, F, K] and [E, K, F]) at load time.  Steps of few tokens stream, for every
 (token, chosen expert) pair, that expert's rows (`ops.moe_up`, `ops.moe_down`): nothing is sorted and nothing comes
 back to the host, so the step sits in a CUDA graph.  Steps of many tokens sort the pairs by expert on the device,
-gather the tokens' rows in that order and run two dense products per expert on its run of rows (the engine's own
-products), which needs the runs' bounds on the host.  The 32-bit engine streams always: a token's result is then the
+gather the tokens' rows in that order, every expert's run into `cap` rows of its own (the longest run, rounded up), and
+run two batched dense products over all experts (the library's, as the engine's other long products are), which needs
+the runs' bounds on the host.  The 32-bit engine streams always: a token's result is then the
 same chain of additions in every step, whatever else the step holds.
 """
 from __future__ import annotations
@@ -74,19 +75,15 @@ class RoutedExperts(Part):
             ops.moe_down(a, self.w_down, idx, wts, y)
             return y
         offsets, place_of, pair_at = ops.moe_sort(idx, self.E)
-        rows = torch.empty((T * top, self.hidden), dtype=h.dtype, device=h.device)
-        ops.moe_gather(h, pair_at, top, rows)
         bounds = offsets.tolist()                        # the one read-back of the step: where every expert's run ends
-        inner = torch.empty((T * top, self.inner), dtype=h.dtype, device=h.device)
-        for e in range(self.E):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                inner[lo:hi] = matmul(rows[lo:hi], self.w_up[e])
+        longest = max(bounds[e + 1] - bounds[e] for e in range(self.E))
+        cap = -(-longest // 64) * 64                     # rows every expert gets in the batched products
+        rows = torch.zeros((self.E * cap, self.hidden), dtype=h.dtype, device=h.device)
+        ops.moe_gather(h, pair_at, idx, offsets, top, rows, cap=cap)
+        inner = torch.bmm(rows.view(self.E, cap, self.hidden), self.w_up.transpose(1, 2))      # [E, cap, F]
+        ops.mark("library product")
         ops.relu_square(inner)
-        outs = torch.empty((T * top, self.hidden), dtype=h.dtype, device=h.device)
-        for e in range(self.E):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                outs[lo:hi] = matmul(inner[lo:hi], self.w_down[e])
-        ops.moe_combine(outs, place_of, wts, y)
+        outs = torch.bmm(inner, self.w_down.transpose(1, 2))                                    # [E, cap, K]
+        ops.mark("library product")
+        ops.moe_combine(outs.view(self.E * cap, self.hidden), place_of, idx, offsets, wts, y, cap=cap)
         return y

@@ -50,8 +50,10 @@ class _MatrixState(Part):
         return -(-self.dv // 16)                         # value columns a block of the scan kernel: ops.scan_columns()
 
     def _state_floats(self) -> int:
-        rows = 4 if self.d <= 32 else 8 if self.d <= 64 else 16 if self.d <= 128 else 32
-        threads = 160 if self.gated else 128             # as the kernel lays a (head, slice) out: ops.scan_state_floats
+        """Floats a (head, slice) of the scan kernel keeps, as `ops.scan_state_floats` says on the device: R rows in each
+        of its threads (IS threads a column, 16 columns and the normaliser's), then m."""
+        rows, per_column = (4, 8) if self.d <= 32 else (8, 8) if self.d <= 64 else (8, 16) if self.d <= 128 else (8, 32)
+        threads = -(-per_column * (17 if self.gated else 16) // 32) * 32
         return rows * threads + (4 if self.gated else 0)
 
     def cache_need(self):
