@@ -56,6 +56,7 @@ template <> __device__ __forceinline__ void warp_dot4<bf16>(const bf16* __restri
         return;
     }
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
     for (int k = lane * 8; k < K; k += 256) {
         uint4 v[4];
 #pragma unroll
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(128) small_proj_kernel(const TA* __restrict__ 
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * ldh + k]);
     __syncthreads();
-    for (int n = wid; n < N; n += 4) {
+    for (int n = blockIdx.y * 4 + wid; n < N; n += gridDim.y * 4) {      // an output a warp
         const float v = warp_dot<TW>(w + (size_t)n * K, xs, K, lane);
         if (lane == 0) out[(size_t)t * ldo + n] = v + (bias ? to_f<TW>(bias[n]) : 0.f);
     }
@@ -97,7 +98,9 @@ TL_EXPORT int tl_small_proj(const void* h, int act_dtype, int ldh, const void* w
     if (T <= 0 || N <= 0) return 0;
     const size_t smem = (size_t)K * sizeof(float);
     if (smem > 48 * 1024) return 1;
-#define SP(TA, TW) small_proj_kernel<TA, TW><<<T, 128, smem, stream>>>((const TA*)h, ldh, (const TW*)w, (const TW*)bias, out, ldo, N, K)
+    // few tokens: the outputs of a token are dealt out to several blocks, so that a step of one token still fills SMs
+    const dim3 grid(T, T >= 512 ? 1 : min((N + 3) / 4, 64));
+#define SP(TA, TW) small_proj_kernel<TA, TW><<<grid, 128, smem, stream>>>((const TA*)h, ldh, (const TW*)w, (const TW*)bias, out, ldo, N, K)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) SP(float, float); else SP(float, bf16); }
     else { if (w_dtype == TL_F32) SP(bf16, float); else SP(bf16, bf16); }
 #undef SP
@@ -144,7 +147,8 @@ TL_EXPORT int tl_topk_softmax(const float* z, int E, int top, int* idx, float* w
 }
 
 // ------------------------------------------------------------------ experts, few tokens
-constexpr int MOE_ROWS = 32;                             // output rows a block (8 a warp)
+constexpr int MOE_ROWS = 16;                             // output rows a block of moe_up (4 a warp, their loads in flight together)
+constexpr int MOE_DOWN_ROWS = 4;                         // output rows a block of moe_down (a warp an expert)
 
 // a[pair, f] = relu(Wup[e][f, :] . h[t, :])^2, pair = t * top + j, e = idx[pair]
 template <typename TA, typename TW>
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * K + k]);
     __syncthreads();
     const TW* w = w_up + (size_t)e * F * K;
-    const int f0 = blockIdx.y * MOE_ROWS + wid * (MOE_ROWS / 4), f1 = min(F, f0 + MOE_ROWS / 4);    // a warp's eight rows
+    const int f0 = blockIdx.y * MOE_ROWS + wid * (MOE_ROWS / 4), f1 = min(F, f0 + MOE_ROWS / 4);    // a warp's four rows
     for (int f = f0; f < f1; f += 4) {                   // four rows at a time: their loads are in flight together
         float u[4];
         warp_dot4<TW>(w + (size_t)f * K, K, min(4, f1 - f), xs, K, lane, u);
@@ -166,28 +170,32 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
     }
 }
 
-// y[t, n] = sum_j wts[t, j] * (Wdown[e_j][n, :] . a[t * top + j, :]), j in the order chosen
+// y[t, n] = sum_j wts[t, j] * (Wdown[e_j][n, :] . a[t * top + j, :]), j in the order chosen.  A block has four rows n of one
+// token; its warps take the chosen experts in turn (warp w: j = w, w + 4, ...), each with its expert's inner row in shared
+// memory of its own, and leave their four products in red[j]; then one thread a row adds them up in the order chosen.
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a, const TW* __restrict__ w_down, const int* __restrict__ idx,
                                                        const float* __restrict__ wts, TA* __restrict__ y, int F, int N, int top) {
-    extern __shared__ float xs[];                        // [top][F]
+    extern __shared__ __align__(16) float xs[];          // [4 warps][F], then red [top][4]
+    float* red = xs + 4 * (size_t)F;
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    for (int k = threadIdx.x; k < top * F; k += blockDim.x) xs[k] = to_f<TA>(a[(size_t)t * top * F + k]);
+    const int n0 = blockIdx.y * MOE_DOWN_ROWS, rows = min(MOE_DOWN_ROWS, N - n0);
+    float* mine = xs + (size_t)wid * F;
+    for (int j = wid; j < top; j += 4) {
+        const int e = idx[(size_t)t * top + j];
+        __syncwarp();
+        for (int k = lane; k < F; k += 32) mine[k] = to_f<TA>(a[((size_t)t * top + j) * F + k]);
+        __syncwarp();
+        float v[4];
+        warp_dot4<TW>(w_down + ((size_t)e * N + n0) * F, F, rows, mine, F, lane, v);
+        const float mv = lane == 0 ? v[0] : lane == 1 ? v[1] : lane == 2 ? v[2] : v[3];
+        if (lane < 4) red[j * 4 + lane] = mv;
+    }
     __syncthreads();
-    const int n0 = blockIdx.y * MOE_ROWS + wid * (MOE_ROWS / 4), n1 = min(N, n0 + MOE_ROWS / 4);    // a warp's eight rows
-    for (int n = n0; n < n1; n += 4) {                   // four rows of one expert at a time, the experts in the order chosen
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < top; ++j) {
-            const int e = idx[(size_t)t * top + j];
-            float v[4];
-            warp_dot4<TW>(w_down + ((size_t)e * N + n) * F, F, min(4, n1 - n), xs + (size_t)j * F, F, lane, v);
-            const float wj = wts[(size_t)t * top + j];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) acc[r] = fmaf(wj, v[r], acc[r]);
-        }
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-            if (lane == 0 && n + r < n1) y[(size_t)t * N + n + r] = from_f<TA>(acc[r]);
+    if (threadIdx.x < rows) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) acc = fmaf(wts[(size_t)t * top + j], red[j * 4 + threadIdx.x], acc);
+        y[(size_t)t * N + n0 + threadIdx.x] = from_f<TA>(acc);
     }
 }
 
@@ -208,9 +216,9 @@ TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dt
 TL_EXPORT int tl_moe_down(const void* a, int act_dtype, const void* w_down, int w_dtype, const int* idx, const float* wts,
                           void* y, int T, int F, int N, int top, cudaStream_t stream) {
     if (T <= 0) return 0;
-    const size_t smem = (size_t)top * F * sizeof(float);
+    const size_t smem = ((size_t)4 * F + (size_t)top * 4) * sizeof(float);
     if (smem > 48 * 1024) return 1;
-    const dim3 grid(T, (N + MOE_ROWS - 1) / MOE_ROWS);
+    const dim3 grid(T, (N + MOE_DOWN_ROWS - 1) / MOE_DOWN_ROWS);
     if (grid.y > 65535) return 1;
 #define MD(TA, TW) moe_down_kernel<TA, TW><<<grid, 128, smem, stream>>>((const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MD(float, float); else MD(float, bf16); }
@@ -278,20 +286,36 @@ __device__ __forceinline__ size_t moe_row(int place, int expert, const int* __re
     return cap ? (size_t)expert * cap + (place - offsets[expert]) : (size_t)place;
 }
 
-// rows[row of place, :] = h[pair_at[place] / top, :]
+// rows[row of place, :] = h[pair_at[place] / top, :].  cap = 0: a block a sorted place.  cap > 0: a block a row of the
+// experts' buffer, (expert, r): the r-th place of the expert's run, or zeros behind the run's end.
 template <typename TA>
-__global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restrict__ pair_at, const int* __restrict__ idx,
-                                  const int* __restrict__ offsets, int cap, TA* __restrict__ rows, int K, int top) {
-    const int pair = pair_at[blockIdx.x];
-    const size_t src = (size_t)(pair / top) * K, dst = moe_row(blockIdx.x, idx[pair], offsets, cap) * K;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) rows[dst + k] = h[src + k];
+__global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restrict__ pair_at, const int* __restrict__ offsets, int cap,
+                                  TA* __restrict__ rows, int K, int top) {
+    int place = blockIdx.x;
+    if (cap) {
+        const int e = blockIdx.x / cap, r = blockIdx.x - e * cap;
+        place = offsets[e] + r < offsets[e + 1] ? offsets[e] + r : -1;
+    }
+    TA* dst = rows + (size_t)blockIdx.x * K;
+    const TA* src = place >= 0 ? h + (size_t)(pair_at[place] / top) * K : nullptr;
+    const bool wide = ((size_t)K * sizeof(TA)) % 16 == 0 && ((((uintptr_t)h) | ((uintptr_t)rows)) & 15) == 0;
+    if (wide) {
+        const int n16 = (int)((size_t)K * sizeof(TA) / 16);
+        for (int k = threadIdx.x; k < n16; k += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[k] = src ? reinterpret_cast<const uint4*>(src)[k] : make_uint4(0, 0, 0, 0);
+    } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = src ? src[k] : from_f<TA>(0.f);
+    }
 }
 
 TL_EXPORT int tl_moe_gather(const void* h, int act_dtype, const int* pair_at, const int* idx, const int* offsets, int cap,
-                            void* rows, int P, int K, int top, cudaStream_t stream) {
-    if (P <= 0) return 0;
-    if (act_dtype == TL_F32) moe_gather_kernel<float><<<P, 256, 0, stream>>>((const float*)h, pair_at, idx, offsets, cap, (float*)rows, K, top);
-    else moe_gather_kernel<bf16><<<P, 256, 0, stream>>>((const bf16*)h, pair_at, idx, offsets, cap, (bf16*)rows, K, top);
+                            void* rows, int P, int E, int K, int top, cudaStream_t stream) {
+    (void)idx;
+    const long long blocks = cap ? (long long)E * cap : P;
+    if (blocks <= 0) return 0;
+    if (blocks > 2147483647LL) return 1;
+    if (act_dtype == TL_F32) moe_gather_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>((const float*)h, pair_at, offsets, cap, (float*)rows, K, top);
+    else moe_gather_kernel<bf16><<<(unsigned)blocks, 128, 0, stream>>>((const bf16*)h, pair_at, offsets, cap, (bf16*)rows, K, top);
     return tl_launch_status();
 }
 
@@ -303,9 +327,28 @@ __global__ void relu_square_kernel(TA* __restrict__ u, size_t n) {
         u[i] = from_f<TA>(v * v);
     }
 }
+// bfloat16, eight values (16 bytes) a thread and step; n8 = n / 8
+__global__ void relu_square_vec8_kernel(uint4* __restrict__ u, size_t n8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 v = u[i];
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float a = fmaxf(__low2float(p[e]), 0.f), b = fmaxf(__high2float(p[e]), 0.f);
+            p[e] = __floats2bfloat162_rn(a * a, b * b);
+        }
+        u[i] = v;
+    }
+}
 
 TL_EXPORT int tl_relu_square(void* u, int act_dtype, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
+    if (act_dtype == TL_BF16 && n % 8 == 0 && (((uintptr_t)u) & 15) == 0) {
+        const long long n8 = n / 8;
+        const int vblocks = (int)((n8 + 255) / 256 < (long long)tl_num_sms() * 32 ? (n8 + 255) / 256 : (long long)tl_num_sms() * 32);
+        relu_square_vec8_kernel<<<vblocks, 256, 0, stream>>>((uint4*)u, (size_t)n8);
+        return tl_launch_status();
+    }
     const int blocks = (int)((n + 255) / 256 < (long long)tl_num_sms() * 16 ? (n + 255) / 256 : (long long)tl_num_sms() * 16);
     if (act_dtype == TL_F32) relu_square_kernel<float><<<blocks, 256, 0, stream>>>((float*)u, (size_t)n);
     else relu_square_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)u, (size_t)n);

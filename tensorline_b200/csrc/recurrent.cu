@@ -83,7 +83,9 @@ __global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_scan_kerne
     const float dec = GATED ? 0.f : A.decay[h];
     const TA* proj = (const TA*)A.proj;
     const int rhalf = A.rot >> 1;
-    for (int i = tid; i < 2 * SCAN_C * TS; i += NT) sm[i] = 0.f;   // rows beyond d and the padding stay zero
+    // rows beyond d and the padding stay zero; a step of single tokens uses (and clears) the first token's part only
+    const int used = min(SCAN_C, t1 - t0) * TS;
+    for (int i = tid; i < used; i += NT) { qs[i] = 0.f; ks[i] = 0.f; }
 
     // The next chunk's q, k, v (as the projection left them) and gate pre-activations wait in registers while this
     // chunk is worked through: their loads are issued before the chunk's arithmetic and used after it.

@@ -38,7 +38,7 @@ _SIGNATURES = {
     "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "tl_moe_sort": [_P, _I, _I, _P, _P, _P, _P],
-    "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _P],
+    "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "tl_relu_square": [_P, _I, ctypes.c_longlong, _P],
     "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
 }
@@ -566,13 +566,13 @@ def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, idx: torch.Tensor, offset
                cap: int = 0) -> None:
     """rows[row of place] = h[pair_at[place] // top].  cap 0: row = place (rows [P, K], the experts' runs one behind the
     other); cap > 0: every expert has cap rows of its own (rows [E * cap, K], row = expert * cap + place - offsets[expert];
-    the rows behind a run are left as they are)."""
+    the rows behind a run are set to zero)."""
     P, K = pair_at.numel(), rows.shape[1]
     E = offsets.numel() - 1
     if h.shape[1] != K or rows.dtype != h.dtype or rows.shape[0] != (E * cap if cap else P) or idx.numel() != P:
         raise KernelError("moe_gather: rows [P, K] (or [E cap, K]) of h's type")
     _contig(h, "h"); _contig(rows, "rows"); _ints(pair_at, "pair_at"); _ints(idx, "idx"); _ints(offsets, "offsets")
-    _check(core().tl_moe_gather(_ptr(h), dtype_code(h.dtype), _ptr(pair_at), _ptr(idx), _ptr(offsets), int(cap), _ptr(rows), P, K,
+    _check(core().tl_moe_gather(_ptr(h), dtype_code(h.dtype), _ptr(pair_at), _ptr(idx), _ptr(offsets), int(cap), _ptr(rows), P, E, K,
                                 int(top), _stream()), "moe_gather")
 
 

@@ -78,7 +78,7 @@ class RoutedExperts(Part):
         bounds = offsets.tolist()                        # the one read-back of the step: where every expert's run ends
         longest = max(bounds[e + 1] - bounds[e] for e in range(self.E))
         cap = -(-longest // 64) * 64                     # rows every expert gets in the batched products
-        rows = torch.zeros((self.E * cap, self.hidden), dtype=h.dtype, device=h.device)
+        rows = torch.empty((self.E * cap, self.hidden), dtype=h.dtype, device=h.device)
         ops.moe_gather(h, pair_at, idx, offsets, top, rows, cap=cap)
         inner = torch.bmm(rows.view(self.E, cap, self.hidden), self.w_up.transpose(1, 2))      # [E, cap, F]
         ops.mark("library product")

@@ -55,10 +55,10 @@ def write_tiny_vutesun(name: str, folder=None, seed: int = 0) -> Path:
         if n.endswith(".sink"):
             tensors[n] = (t.float() * 15.0 + 0.5).to(t.dtype)        # of the order of the scores: some heads lose half their weight
         elif n.endswith((".i.b", ".f.b")):
-            tensors[n] = (t.float() * 8.0 + (2.0 if n.endswith(".f.b") else -1.0)).to(t.dtype)
+            tensors[n] = (t.float() * 4.0 + (2.0 if n.endswith(".f.b") else -1.0)).to(t.dtype)
         elif n.endswith(".b"):
             tensors[n] = (t.float() * 4.0).to(t.dtype)
         elif n.endswith((".i", ".f")):
-            tensors[n] = (t.float() * 3.0).to(t.dtype)              # gates that move from token to token
+            tensors[n] = (t.float() * 1.5).to(t.dtype)              # gates that move from token to token
     write_safetensors(folder / "model.safetensors", tensors, {"format": "pt"})
     return folder
