@@ -87,26 +87,43 @@ __global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_scan_kerne
     const int used = min(SCAN_C, t1 - t0) * TS;
     for (int i = tid; i < used; i += NT) { qs[i] = 0.f; ks[i] = 0.f; }
 
-    // The next chunk's q, k, v (as the projection left them) and gate pre-activations wait in registers while this
-    // chunk is worked through: their loads are issued before the chunk's arithmetic and used after it.
-    float fq[PF], fk[PF], fv[PV], fgi = 0.f, fgf = 0.f;
+    // Which elements of a chunk this thread moves never changes: token and dimension of each, its place in the chunk's rows
+    // of the projection and in shared memory, worked out once.
+    int g_off[PF], s_off[PF], v_goff[PV];
+    unsigned in_rot = 0, v_ok = 0;                         // bit it: the element is rotated / the v element exists
+    int tok_of[PF];
+#pragma unroll
+    for (int it = 0; it < PF; ++it) {
+        const int idx = tid + it * NT, t = idx / d, e = idx - t * d;
+        tok_of[it] = t < SCAN_C ? t : SCAN_C;              // SCAN_C: beyond every chunk
+        g_off[it] = t * A.stride + h * d + e;
+        s_off[it] = t * TS + (e / R) * RS + (e % R);
+        if (e < A.rot) in_rot |= 1u << it;
+    }
+#pragma unroll
+    for (int it = 0; it < PV; ++it) {
+        const int idx = tid + it * NT, t = idx / SCAN_JS, col = z * SCAN_JS + (idx - t * SCAN_JS);
+        v_goff[it] = t * A.stride + A.v_off + h * A.dv + col;
+        if (t < SCAN_C && col < A.dv) v_ok |= 1u << it;
+    }
+    float* freq = nq + SCAN_C;                             // [rot / 2]
+    for (int i = tid; i < rhalf; i += NT) freq[i] = A.inv_freq[i];
+    const int pos0 = t0 < t1 ? A.pos[t0] : 0;              // a request's tokens of a step are consecutive positions
+
+    // The next chunk's q, k, v (as the projection left them) and gate pre-activations wait in registers, unconverted, while
+    // this chunk is worked through: their loads are issued before the chunk's arithmetic and first used after it.
+    TA fq[PF], fk[PF], fv[PV];
+    float fgi = 0.f, fgf = 0.f;
     auto fetch = [&](int c0) {
         const int n = min(SCAN_C, t1 - c0);
+        const TA* base = proj + (size_t)c0 * A.stride;
 #pragma unroll
         for (int it = 0; it < PF; ++it) {
-            const int idx = tid + it * NT, t = idx / d, e = idx - t * d;
-            fq[it] = fk[it] = 0.f;
-            if (t < n) {
-                const TA* row = proj + (size_t)(c0 + t) * A.stride + (size_t)h * d + e;
-                fq[it] = to_f<TA>(row[A.q_off]);
-                fk[it] = to_f<TA>(row[A.k_off]);
-            }
+            if (tok_of[it] < n) { fq[it] = base[g_off[it] + A.q_off]; fk[it] = base[g_off[it] + A.k_off]; }
         }
 #pragma unroll
-        for (int it = 0; it < PV; ++it) {
-            const int idx = tid + it * NT, t = idx / SCAN_JS, col = z * SCAN_JS + (idx - t * SCAN_JS);
-            fv[it] = (t < n && col < A.dv) ? to_f<TA>(proj[(size_t)(c0 + t) * A.stride + A.v_off + (size_t)h * A.dv + col]) : 0.f;
-        }
+        for (int it = 0; it < PV; ++it)
+            if (((v_ok >> it) & 1u) && (tid + it * NT) / SCAN_JS < n) fv[it] = base[v_goff[it]];
         if (GATED && tid < n) {
             const float* g = A.gates + (size_t)(c0 + tid) * 2 * A.H;
             fgi = g[h]; fgf = g[A.H + h];
@@ -122,16 +139,16 @@ __global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_scan_kerne
         // the chunk into shared memory; dimensions that are not rotated get their scale here
 #pragma unroll
         for (int it = 0; it < PF; ++it) {
-            const int idx = tid + it * NT, t = idx / d, e = idx - t * d;
-            if (t < n) {
-                qs[at(t, e)] = e < A.rot ? fq[it] : fq[it] * A.q_scale;
-                ks[at(t, e)] = e < A.rot ? fk[it] : fk[it] * A.k_scale;
+            if (tok_of[it] < n) {
+                const bool rt = (in_rot >> it) & 1u;
+                qs[s_off[it]] = rt ? to_f<TA>(fq[it]) : to_f<TA>(fq[it]) * A.q_scale;
+                ks[s_off[it]] = rt ? to_f<TA>(fk[it]) : to_f<TA>(fk[it]) * A.k_scale;
             }
         }
 #pragma unroll
         for (int it = 0; it < PV; ++it) {
             const int idx = tid + it * NT;
-            if (idx < n * SCAN_JS) vs[idx] = fv[it];
+            if (idx < n * SCAN_JS) vs[idx] = ((v_ok >> it) & 1u) ? to_f<TA>(fv[it]) : 0.f;
         }
         if (GATED && tid < n) {
             gb[tid] = A.cap * tanhf(fgi / A.cap);
@@ -143,7 +160,7 @@ __global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_scan_kerne
             const int t = p / rhalf, i = p - t * rhalf;
             const int e1 = at(t, A.interleaved ? 2 * i : i), e2 = at(t, A.interleaved ? 2 * i + 1 : i + rhalf);
             float sn, cs;
-            sincosf(__fmul_rn((float)A.pos[c0 + t], A.inv_freq[i]), &sn, &cs);
+            sincosf(__fmul_rn((float)(pos0 + (c0 - t0) + t), freq[i]), &sn, &cs);
             const float q1 = qs[e1], q2 = qs[e2], k1 = ks[e1], k2 = ks[e2];
             qs[e1] = (__fmul_rn(q1, cs) - __fmul_rn(q2, sn)) * A.q_scale;
             qs[e2] = (__fmul_rn(q2, cs) + __fmul_rn(q1, sn)) * A.q_scale;
@@ -221,6 +238,90 @@ __global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_scan_kerne
     if (GATED && tid == 0) st[R * NT] = m_run;
 }
 
+// The same recurrence for a step of single tokens (decoding): one token a request, so none of the chunk machinery; a
+// block loads its part of the state, brings the token's q and k into shared memory (rotated and scaled by the scan
+// kernel's own arithmetic, so a token decoded alone gets the bits it gets inside a portion), works the token in and
+// stores the state.  Few registers: several blocks share an SM and the loads and stores of the state, which are all
+// the step moves, overlap.
+template <typename TA, int R, int IS, bool GATED>
+__global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_step_kernel(const ScanArgs A) {
+    using Sh = ScanShape<R, IS, GATED>;
+    constexpr int NT = Sh::NT, PB = Sh::PB, RS = Sh::RS, TS = Sh::TS;
+    __shared__ __align__(16) float qs[TS];
+    __shared__ __align__(16) float ks[TS];
+    __shared__ float sc[4];                                // a, b, m after the token, n . q
+    const int d = A.d;
+    const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+    const int tid = threadIdx.x, islice = tid % IS, j = tid / IS;
+    const int t = A.q_start[b];
+    float* st = A.state + (size_t)A.slots[b] * A.slot_stride + ((size_t)h * gridDim.z + z) * PB;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) S[r] = st[r * NT + tid];
+    const float m_run = GATED ? st[R * NT] : 0.f;
+    const int jcol = z * SCAN_JS + j;
+    const bool ones = GATED && j == SCAN_JS;
+    const bool live = j < SCAN_JS && jcol < A.dv;
+    const TA* row = (const TA*)A.proj + (size_t)t * A.stride;
+    const int rhalf = A.rot >> 1;
+    const float vraw = live ? to_f<TA>(row[A.v_off + (size_t)h * A.dv + jcol]) : 0.f;
+    for (int e = tid; e < R * IS; e += NT) {
+        float qv = 0.f, kv = 0.f;
+        if (e < d) {
+            qv = to_f<TA>(row[A.q_off + (size_t)h * d + e]); kv = to_f<TA>(row[A.k_off + (size_t)h * d + e]);
+            if (e >= A.rot) { qv *= A.q_scale; kv *= A.k_scale; }
+        }
+        qs[(e / R) * RS + (e % R)] = qv; ks[(e / R) * RS + (e % R)] = kv;
+    }
+    if (GATED && tid == 0) {
+        const float* g = A.gates + (size_t)t * 2 * A.H;
+        const float gi = A.cap * tanhf(g[h] / A.cap);
+        const float gf = log_sigmoid(A.cap * tanhf(g[A.H + h] / A.cap));
+        const float m = fmaxf(gf + m_run, gi);
+        sc[0] = expf(gf + m_run - m); sc[1] = expf(gi - m); sc[2] = m;
+    }
+    __syncthreads();
+    if (rhalf) {
+        const int p0 = A.pos[t];
+        for (int i = tid; i < rhalf; i += NT) {
+            const int a1 = A.interleaved ? 2 * i : i, a2 = A.interleaved ? 2 * i + 1 : i + rhalf;
+            const int e1 = (a1 / R) * RS + (a1 % R), e2 = (a2 / R) * RS + (a2 % R);
+            float sn, cs;
+            sincosf(__fmul_rn((float)p0, A.inv_freq[i]), &sn, &cs);
+            const float q1 = qs[e1], q2 = qs[e2], k1 = ks[e1], k2 = ks[e2];
+            qs[e1] = (__fmul_rn(q1, cs) - __fmul_rn(q2, sn)) * A.q_scale;
+            qs[e2] = (__fmul_rn(q2, cs) + __fmul_rn(q1, sn)) * A.q_scale;
+            ks[e1] = (__fmul_rn(k1, cs) - __fmul_rn(k2, sn)) * A.k_scale;
+            ks[e2] = (__fmul_rn(k2, cs) + __fmul_rn(k1, sn)) * A.k_scale;
+        }
+        __syncthreads();
+    }
+    const float a = GATED ? sc[0] : A.decay[h];
+    const float v = ones ? 1.f : vraw;
+    const float bv = GATED ? sc[1] * v : v;
+    float acc = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; r += 4) {
+        const float4 kk = *reinterpret_cast<const float4*>(ks + islice * RS + r);
+        const float4 qq = *reinterpret_cast<const float4*>(qs + islice * RS + r);
+        S[r] = fmaf(a, S[r], kk.x * bv);         acc = fmaf(S[r], qq.x, acc);
+        S[r + 1] = fmaf(a, S[r + 1], kk.y * bv); acc = fmaf(S[r + 1], qq.y, acc);
+        S[r + 2] = fmaf(a, S[r + 2], kk.z * bv); acc = fmaf(S[r + 2], qq.z, acc);
+        S[r + 3] = fmaf(a, S[r + 3], kk.w * bv); acc = fmaf(S[r + 3], qq.w, acc);
+    }
+#pragma unroll
+    for (int o = 1; o < IS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+#pragma unroll
+    for (int r = 0; r < R; ++r) st[r * NT + tid] = S[r];
+    if (GATED) {
+        if (ones && islice == 0) sc[3] = acc;
+        if (tid == 0) st[R * NT] = sc[2];
+        __syncthreads();
+        acc = acc / (fmaxf(fabsf(sc[3]), expf(-sc[2])) + A.den_eps);
+    }
+    if (live && islice == 0) A.out[(size_t)t * A.H * A.dv + (size_t)h * A.dv + jcol] = acc;
+}
+
 // How a head of d rows is dealt out: 0: R 4 x IS 8 (d <= 32), 1: 8 x 8 (<= 64), 2: 8 x 16 (<= 128), 3: 8 x 32 (<= 256); -1: too large.
 static int scan_shape(int d) { return d <= 32 ? 0 : d <= 64 ? 1 : d <= 128 ? 2 : d <= 256 ? 3 : -1; }
 
@@ -237,10 +338,14 @@ TL_EXPORT int tl_scan_state_floats(int d, int gated) {
 TL_EXPORT int tl_scan_columns() { return SCAN_JS; }
 
 template <typename TA, int R, int IS, bool GATED>
-static int launch_scan_shape(const ScanArgs& A, int B, cudaStream_t stream) {
+static int launch_scan_shape(const ScanArgs& A, int B, bool single, cudaStream_t stream) {
     using Sh = ScanShape<R, IS, GATED>;
     const int nz = (A.dv + SCAN_JS - 1) / SCAN_JS;
-    const size_t smem = (size_t)(2 * SCAN_C * Sh::TS + SCAN_C * SCAN_JS + 4 * SCAN_C) * sizeof(float);
+    if (single) {
+        linear_step_kernel<TA, R, IS, GATED><<<dim3(B, A.H, nz), Sh::NT, 0, stream>>>(A);
+        return tl_launch_status();
+    }
+    const size_t smem = (size_t)(2 * SCAN_C * Sh::TS + SCAN_C * SCAN_JS + 4 * SCAN_C + A.rot / 2) * sizeof(float);
     if (smem > 48 * 1024) {                              // the widest heads: more dynamic shared memory than a kernel has by default
         static bool raised[TL_MAX_DEVICES] = {};
         const int dev = tl_device_index();
@@ -256,12 +361,12 @@ static int launch_scan_shape(const ScanArgs& A, int B, cudaStream_t stream) {
 }
 
 template <typename TA, bool GATED>
-static int launch_scan(const ScanArgs& A, int B, cudaStream_t stream) {
+static int launch_scan(const ScanArgs& A, int B, bool single, cudaStream_t stream) {
     switch (scan_shape(A.d)) {
-        case 0: return launch_scan_shape<TA, 4, 8, GATED>(A, B, stream);
-        case 1: return launch_scan_shape<TA, 8, 8, GATED>(A, B, stream);
-        case 2: return launch_scan_shape<TA, 8, 16, GATED>(A, B, stream);
-        case 3: return launch_scan_shape<TA, 8, 32, GATED>(A, B, stream);
+        case 0: return launch_scan_shape<TA, 4, 8, GATED>(A, B, single, stream);
+        case 1: return launch_scan_shape<TA, 8, 8, GATED>(A, B, single, stream);
+        case 2: return launch_scan_shape<TA, 8, 16, GATED>(A, B, single, stream);
+        case 3: return launch_scan_shape<TA, 8, 32, GATED>(A, B, single, stream);
     }
     return 1;
 }
@@ -270,14 +375,16 @@ TL_EXPORT int tl_linear_scan(const void* proj, int act_dtype, int stride, int q_
                              const float* gates, float cap, const float* decay, const float* inv_freq, int rot,
                              int interleaved, const int* pos, float q_scale, float k_scale, float* state,
                              long long slot_stride, const int* q_start, const int* slots, float* out, int B, int H,
-                             int d, int dv, float den_eps, cudaStream_t stream) {
+                             int d, int dv, float den_eps, int single_tokens, cudaStream_t stream) {
+    // single_tokens: every request of the step brings exactly one token (the caller knows; the step kernel takes it)
     if (B <= 0 || H <= 0) return 0;
     if (H > 65535 || (rot & 1) || rot > d) return 1;
     const ScanArgs A{proj, stride, q_off, k_off, v_off, gates, cap, decay, inv_freq, rot, interleaved, pos, q_scale, k_scale,
                      state, slot_stride, q_start, slots, out, H, d, dv, den_eps};
     const bool gated = gates != nullptr;
-    if (act_dtype == TL_F32) return gated ? launch_scan<float, true>(A, B, stream) : launch_scan<float, false>(A, B, stream);
-    return gated ? launch_scan<bf16, true>(A, B, stream) : launch_scan<bf16, false>(A, B, stream);
+    const bool single = single_tokens != 0;
+    if (act_dtype == TL_F32) return gated ? launch_scan<float, true>(A, B, single, stream) : launch_scan<float, false>(A, B, single, stream);
+    return gated ? launch_scan<bf16, true>(A, B, single, stream) : launch_scan<bf16, false>(A, B, single, stream);
 }
 
 // ------------------------------------------------------------------ per-head RMS norm, weight, gate

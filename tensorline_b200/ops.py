@@ -28,7 +28,7 @@ _SIGNATURES = {
     "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
     "tl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "tl_linear_scan": [_P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P, _F, _F, _P, ctypes.c_longlong, _P, _P, _P, _I, _I,
-                       _I, _I, _F, _P],
+                       _I, _I, _F, _I, _P],
     "tl_scan_state_floats": [_I, _I],
     "tl_scan_columns": [],
     "tl_head_norm_gate": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
@@ -430,17 +430,20 @@ def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, H: int, 
                 q_start: torch.Tensor, slots: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, *, B: int,
                 decay: torch.Tensor | None = None, gates: torch.Tensor | None = None, cap: float = 1.0,
                 inv_freq: torch.Tensor | None = None, rot: int = 0, pairing: str = "half", q_scale: float = 1.0,
-                k_scale: float = 1.0, den_eps: float = 0.0) -> None:
+                k_scale: float = 1.0, den_eps: float = 0.0, single_tokens: bool = False) -> None:
     """S_t = a_t S_(t-1) + b_t k_t v_t^T and o_t = S_t^T q_t per (request, head), tokens of a request in order, the state
     read from and left in `state[slot]` (float32, one row a slot, in the kernel's own layout: `scan_state_floats`).
     q, k [H, d] and v [H, dv] of token t are at `proj[t, q_off:]`, `proj[t, k_off:]`, `proj[t, v_off:]`.
     `decay` (float32 [H]): a_t = decay[h], b_t = 1.  `gates` (float32 [T, 2H], input then forget pre-activations): the
     capped log gates with a running maximum, a normaliser, and o_t divided by max(|n_t . q_t|, exp(-m_t)) + den_eps.
-    q and k are rotated by `pos` over their first `rot` dimensions (`inv_freq` float32 [rot/2]) and scaled.  out float32
-    [T, H * dv]."""
+    q and k are rotated by `pos` over their first `rot` dimensions (`inv_freq` float32 [rot/2]) and scaled; a request's
+    tokens of the step stand at consecutive positions (the kernel reads the first one's).  out float32 [T, H * dv].
+    `single_tokens`: every request brings exactly one token (T == B): the step kernel, which gives the scan kernel's bits."""
     T = proj.shape[0]
     if (decay is None) == (gates is None):
         raise KernelError("linear_scan: either a fixed decay per head or gate pre-activations")
+    if single_tokens and T != B:
+        raise KernelError("linear_scan: a step of single tokens has as many rows as requests")
     _contig(proj, "proj"); _ints(q_start, "q_start"); _ints(slots, "slots"); _ints(pos, "pos"); _contig(state, "state"); _contig(out, "out")
     if out.dtype != torch.float32 or out.shape != (T, H * dv) or state.dtype != torch.float32:
         raise KernelError("linear_scan: out must be float32 [T, H * dv] and the state float32")
@@ -462,7 +465,8 @@ def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, H: int, 
     _check(core().tl_linear_scan(_ptr(proj), dtype_code(proj.dtype), proj.shape[1], q_off, k_off, v_off, _ptr(gates), float(cap),
                                  _ptr(decay), _ptr(inv_freq) if rot else None, int(rot), int(pairing == "interleaved"), _ptr(pos),
                                  float(q_scale), float(k_scale), _ptr(state), per_slot, _ptr(q_start), _ptr(slots), _ptr(out),
-                                 int(B), H, d, dv, float(den_eps), _stream()), "linear_scan")
+                                 int(B), H, d, dv, float(den_eps), int(single_tokens), _stream()),
+           "linear_step" if single_tokens else "linear_scan")
 
 
 _ACTS = {None: 0, "sigmoid": 1, "silu": 2}

@@ -113,7 +113,7 @@ class Retention(_MatrixState):
             rotary = Rotary(*rotary)
         ops.linear_scan(proj, 0, H * d, 2 * H * d, H, d, dv, state, ctx.q_start, ctx.slots, ctx.pos, o, B=ctx.B,
                         decay=self.decay, inv_freq=rotary.inv_freq, rot=rotary.rot, pairing=rotary.pairing,
-                        k_scale=d ** -0.5)
+                        k_scale=d ** -0.5, single_tokens=ctx.decode_only)
 
 
 @register_mixer("mlstm")
@@ -153,4 +153,4 @@ class MLSTM(_MatrixState):
         gates = torch.empty((h.shape[0], 2 * H), dtype=torch.float32, device=h.device)
         ops.small_proj(h, self.w_gates, self.b_gates, gates)
         ops.linear_scan(proj, 0, H * d, 2 * H * d, H, d, dv, state, ctx.q_start, ctx.slots, ctx.pos, o, B=ctx.B,
-                        gates=gates, cap=self.cap, q_scale=d ** -0.5, den_eps=1e-6)
+                        gates=gates, cap=self.cap, q_scale=d ** -0.5, den_eps=1e-6, single_tokens=ctx.decode_only)

@@ -97,7 +97,7 @@ def test_linear_scan_in_one_step_and_in_portions(adt, case):
     per_slot = H * -(-dv // ops.scan_columns()) * ops.scan_state_floats(d, gated)
     slots = [5, 0, 3, 2][:B]
 
-    def run(cuts):
+    def run(cuts, single=False):
         state = torch.zeros(7, per_slot, device="cuda")
         state[1] = 7.0                                          # a slot nobody owns: must stay as it is
         out = torch.zeros(T, H * dv, device="cuda")
@@ -118,7 +118,7 @@ def test_linear_scan_in_one_step_and_in_portions(adt, case):
             if gated:
                 step_kw["gates"] = gates[idx].contiguous().cuda()
             ops.linear_scan(proj[idx].contiguous().cuda(), 0, H * d, 2 * H * d, H, d, dv, state, i32(q_start), i32(live),
-                            pos[idx].to(torch.int32).cuda(), part, B=len(live), **step_kw)
+                            pos[idx].to(torch.int32).cuda(), part, B=len(live), single_tokens=single and len(rows) == len(live), **step_kw)
             out[idx.cuda()] = part
         assert all(done[b] == lens[b] for b in range(B))
         assert torch.all(state[1] == 7.0)
@@ -129,6 +129,9 @@ def test_linear_scan_in_one_step_and_in_portions(adt, case):
     assert_close(whole.view(T, H, dv), want, "scan, whole requests", **tol)
     cuts = [[7, 1, 2, 16], [1, 0, 1, 1], [16, 0, 2, 17], [2, 5, 0, 3], [1, 1, 1, 1]] + [[33, 33, 33, 33]] * 6
     assert torch.equal(run([c[:B] for c in cuts]), whole), "portions give other bits than the whole requests"
+    # the same cuts with the steps of single tokens through the step kernel, then every token alone through it
+    assert torch.equal(run([c[:B] for c in cuts], single=True), whole), "the step kernel gives other bits than the scan kernel"
+    assert torch.equal(run([[1] * B] * max(lens), single=True), whole), "token by token gives other bits"
 
 
 def test_linear_scan_keeps_a_far_token():
