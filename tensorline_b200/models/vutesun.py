@@ -41,7 +41,7 @@ def describe_vutesun(cfg: VutesunConfig) -> ModelSpec:
         if layer.mlp is not None:
             ff = PartSpec("routed_experts", {"hidden": W, "inner": layer.mlp.ff, "experts": layer.mlp.experts,
                                              "top": layer.mlp.top, "activation": "relu_squared"})
-        block = PartSpec("pre_norm", {"mixer": mixer, "feed_forward": ff, "norm1": norm, "norm2": norm if ff is not None else None,
+        block = PartSpec("pre_norm", {"mixer": mixer, "feed_forward": ff, "norm1": norm, "norm2": norm,
                                       "residual_scale": cfg.residual_mult,
                                       "names": {"norm1": "norm1", "mixer": "mix", "norm2": "norm2", "feed_forward": "mlp"}})
         layers.append(LayerSpec(block, f"l{i}"))

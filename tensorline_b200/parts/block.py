@@ -21,7 +21,8 @@ class PreNormBlock(Part):
         super().__init__(rt)
         self.norm1 = NORMS.build(norm1, rt)
         self.mixer = MIXERS.build(mixer, rt)
-        self.norm2 = NORMS.build(norm2, rt) if feed_forward is not None else None
+        # a layer without a feed-forward has no use for a second norm; a stored one is accepted and left alone
+        self.norm2 = NORMS.build(norm2, rt) if norm2 is not None else None
         self.ff = FEED_FORWARDS.build(feed_forward, rt) if feed_forward is not None else None
         self.residual_scale = float(residual_scale)
         # names of the sub-parts inside the layer's tensor prefix
@@ -35,13 +36,19 @@ class PreNormBlock(Part):
         return tuple((part, p) for part, p in parts if part is not None)
 
     def expected_tensors(self, prefix):
+        import dataclasses
         out = {}
         for part, p in self._children(prefix):
-            out.update(part.expected_tensors(p))
+            specs = part.expected_tensors(p)
+            if part is self.norm2 and self.ff is None:
+                specs = {k: dataclasses.replace(v, optional=True) for k, v in specs.items()}
+            out.update(specs)
         return out
 
     def bind(self, weights, prefix):
         for part, p in self._children(prefix):
+            if part is self.norm2 and self.ff is None:
+                continue
             part.bind(weights, p)
 
     def cache_need(self):
@@ -49,7 +56,8 @@ class PreNormBlock(Part):
 
     @property
     def graph_capturable(self) -> bool:
-        return all(part.graph_capturable for part in (self.norm1, self.mixer, self.norm2, self.ff) if part is not None)
+        return all(part.graph_capturable for part in (self.norm1, self.mixer, self.norm2 if self.ff is not None else None, self.ff)
+                   if part is not None)
 
     def forward(self, x, pending, ctx, cache):
         # a norm that supports it hands a part that says it can take one (`accepts_normed_input`) the recipe of its

@@ -439,3 +439,21 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(model):
         assert got == want, f"graphs {graphs}: {got} != {want}"
         st = eng.stats()
         assert st["free_pages"] == st["num_pages"] and st["max_running_seen"] == 3 and (st["graph_replays"] > 0) == graphs
+
+
+@pytest.mark.parametrize("name", ["V3", "V4"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_further_shapes_of_the_design(name, dtype, tmp_path):
+    """Recurrences only (no page group at all); attention without rotation, with as many KV heads as query heads and one
+    head; every expert chosen; a decay of one: whole requests and changing portions against the plain model."""
+    folder = write_tiny_vutesun(name, tmp_path / name)
+    plain = PlainVutesun(folder)
+    V = CONFIGS[name]["vocab"]
+    reqs = {f"r{i}": random_tokens(V, n, seed=300 + i) for i, n in enumerate([3, 50, 1, 81])}
+    m = dict(name=name, folder=folder, reqs=reqs, want={r: forward(plain, t) for r, t in reqs.items()}, page=PAGE_SIZE[name], vocab=V)
+    whole = replay(m, dtype, steps_alone(m, cuts_whole), max_tokens=128)
+    check(m, dtype, whole, "whole")
+    cut = replay(m, dtype, steps_alone(m, cuts_changing), max_tokens=128)
+    check(m, dtype, cut, "changing portions")
+    if dtype == "float32":
+        assert all(torch.equal(cut[k], whole[k]) for k in whole)

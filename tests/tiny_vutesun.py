@@ -40,8 +40,22 @@ V2 = {"architecture": "Vutesun", "vocab": 90, "width": 72, "norm": {"eps": 1e-5}
     {"type": "mlstm", "mixer": {"heads": 1, "dim": 40, "vdim": 72, "gate_cap": 15.0}, "mlp": None},
     {"type": "mlstm", "mixer": {"heads": 2, "dim": 136, "vdim": 8, "gate_cap": 3.0}, "mlp": _moe(16, 2, 2)},
 ]}
-CONFIGS = {"V1": V1, "V2": V2}
-PAGE_SIZE = {"V1": 8, "V2": 16}
+# recurrences only: no keys or values anywhere, so no page group at all
+V3 = {"architecture": "Vutesun", "vocab": 77, "width": 40, "norm": {"eps": 1e-5}, "residual_mult": 1.3, "layers": [
+    {"type": "mlstm", "mixer": {"heads": 2, "dim": 20, "vdim": 12, "gate_cap": 10.0}, "mlp": None},
+    {"type": "mlstm", "mixer": {"heads": 5, "dim": 8, "vdim": 8, "gate_cap": 15.0}, "mlp": _moe(32, 4, 4)},
+]}
+# attention without rotation and with as many KV heads as query heads beside a retention of full rotation; every expert chosen
+V4 = {"architecture": "Vutesun", "vocab": 64, "width": 32, "norm": {"eps": 1e-6}, "residual_mult": 0.9, "layers": [
+    {"type": "parallel", "mixer": {
+        "left": {"heads": 3, "kv_heads": 3, "dim": 16, "vdim": 8, "scale": 0.25, "rot": {"base": 10.0, "dims": 0}},
+        "right": {"heads": 2, "dim": 8, "vdim": 16, "decay": [0.5, 1.0], "rot": {"base": 10.0, "dims": 8}}}, "mlp": _moe(8, 3, 3)},
+    {"type": "parallel", "mixer": {
+        "left": {"heads": 1, "kv_heads": 1, "dim": 48, "vdim": 48, "scale": 0.2, "rot": {"base": 1e4, "dims": 2}},
+        "right": {"heads": 1, "dim": 4, "vdim": 4, "decay": [0.9], "rot": {"base": 2.0, "dims": 2}}}, "mlp": None},
+]}
+CONFIGS = {"V1": V1, "V2": V2, "V3": V3, "V4": V4}
+PAGE_SIZE = {"V1": 8, "V2": 16, "V3": 4, "V4": 16}
 
 
 def write_tiny_vutesun(name: str, folder=None, seed: int = 0) -> Path:
