@@ -85,6 +85,8 @@ __global__ void __launch_bounds__(128) small_proj_kernel(const TA* __restrict__ 
                                                          const TW* __restrict__ bias, float* __restrict__ out, int ldo, int N, int K) {
     extern __shared__ float xs[];
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
+    grid_dependency_trigger();
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * ldh + k]);
     __syncthreads();
     for (int n = blockIdx.y * 4 + wid; n < N; n += gridDim.y * 4) {      // an output a warp
@@ -100,7 +102,7 @@ TL_EXPORT int tl_small_proj(const void* h, int act_dtype, int ldh, const void* w
     if (smem > 48 * 1024) return 1;
     // few tokens: the outputs of a token are dealt out to several blocks, so that a step of one token still fills SMs
     const dim3 grid(T, T >= 512 ? 1 : min((N + 3) / 4, 64));
-#define SP(TA, TW) small_proj_kernel<TA, TW><<<grid, 128, smem, stream>>>((const TA*)h, ldh, (const TW*)w, (const TW*)bias, out, ldo, N, K)
+#define SP(TA, TW) launch_after_wait(small_proj_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, ldh, (const TW*)w, (const TW*)bias, out, ldo, N, K)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) SP(float, float); else SP(float, bf16); }
     else { if (w_dtype == TL_F32) SP(bf16, float); else SP(bf16, bf16); }
 #undef SP
@@ -113,6 +115,8 @@ TL_EXPORT int tl_small_proj(const void* h, int act_dtype, int ldh, const void* w
 __global__ void __launch_bounds__(128) topk_softmax_kernel(const float* __restrict__ z, int E, int top, int* __restrict__ idx,
                                                            float* __restrict__ wts, int T) {
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
+    grid_dependency_trigger();
     if (t >= T) return;
     const float* row = z + (size_t)t * E;
     unsigned taken = 0;                                  // bit c: my element lane + 32 c is chosen
@@ -142,7 +146,7 @@ __global__ void __launch_bounds__(128) topk_softmax_kernel(const float* __restri
 TL_EXPORT int tl_topk_softmax(const float* z, int E, int top, int* idx, float* wts, int T, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E > 1024 || top > 32 || top > E || top < 1) return 1;
-    topk_softmax_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, E, top, idx, wts, T);
+    launch_after_wait(topk_softmax_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, z, E, top, idx, wts, T);
     return tl_launch_status();
 }
 
@@ -156,6 +160,8 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
                                                      TA* __restrict__ a, int K, int F, int top) {
     extern __shared__ float xs[];
     const int pair = blockIdx.x, t = pair / top, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
+    grid_dependency_trigger();
     const int e = idx[pair];
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * K + k]);
     __syncthreads();
@@ -181,6 +187,8 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a,
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int n0 = blockIdx.y * MOE_DOWN_ROWS, rows = min(MOE_DOWN_ROWS, N - n0);
     float* mine = xs + (size_t)wid * F;
+    grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
+    grid_dependency_trigger();
     for (int j = wid; j < top; j += 4) {
         const int e = idx[(size_t)t * top + j];
         __syncwarp();
@@ -206,7 +214,7 @@ TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dt
     if (smem > 48 * 1024) return 1;
     const dim3 grid(P, (F + MOE_ROWS - 1) / MOE_ROWS);
     if (grid.y > 65535) return 1;
-#define MU(TA, TW) moe_up_kernel<TA, TW><<<grid, 128, smem, stream>>>((const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top)
+#define MU(TA, TW) launch_after_wait(moe_up_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MU(float, float); else MU(float, bf16); }
     else { if (w_dtype == TL_F32) MU(bf16, float); else MU(bf16, bf16); }
 #undef MU
@@ -220,7 +228,7 @@ TL_EXPORT int tl_moe_down(const void* a, int act_dtype, const void* w_down, int 
     if (smem > 48 * 1024) return 1;
     const dim3 grid(T, (N + MOE_DOWN_ROWS - 1) / MOE_DOWN_ROWS);
     if (grid.y > 65535) return 1;
-#define MD(TA, TW) moe_down_kernel<TA, TW><<<grid, 128, smem, stream>>>((const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top)
+#define MD(TA, TW) launch_after_wait(moe_down_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MD(float, float); else MD(float, bf16); }
     else { if (w_dtype == TL_F32) MD(bf16, float); else MD(bf16, bf16); }
 #undef MD

@@ -253,6 +253,8 @@ __global__ void __launch_bounds__(ScanShape<R, IS, GATED>::NT) linear_step_kerne
     const int d = A.d;
     const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
     const int tid = threadIdx.x, islice = tid % IS, j = tid / IS;
+    grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
+    grid_dependency_trigger();
     const int t = A.q_start[b];
     float* st = A.state + (size_t)A.slots[b] * A.slot_stride + ((size_t)h * gridDim.z + z) * PB;
     float S[R];
@@ -342,8 +344,7 @@ static int launch_scan_shape(const ScanArgs& A, int B, bool single, cudaStream_t
     using Sh = ScanShape<R, IS, GATED>;
     const int nz = (A.dv + SCAN_JS - 1) / SCAN_JS;
     if (single) {
-        linear_step_kernel<TA, R, IS, GATED><<<dim3(B, A.H, nz), Sh::NT, 0, stream>>>(A);
-        return tl_launch_status();
+        return launch_after_wait(linear_step_kernel<TA, R, IS, GATED>, dim3(B, A.H, nz), dim3(Sh::NT), 0, stream, A);
     }
     const size_t smem = (size_t)(2 * SCAN_C * Sh::TS + SCAN_C * SCAN_JS + 4 * SCAN_C + A.rot / 2) * sizeof(float);
     if (smem > 48 * 1024) {                              // the widest heads: more dynamic shared memory than a kernel has by default
@@ -394,6 +395,8 @@ template <typename TA, typename TW>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const TA* __restrict__ g, int g_stride,
                                       const TW* __restrict__ w, TA* __restrict__ out, int H, int dv, float eps, int act) {
     const int t = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
+    grid_dependency_trigger();
     if (h >= H) return;
     const float* row = o + ((size_t)t * H + h) * dv;
     float ss = 0.f;
@@ -416,7 +419,7 @@ TL_EXPORT int tl_head_norm_gate(const float* o, const void* g, int g_stride, con
                                 int act_dtype, int T, int H, int dv, float eps, int act, cudaStream_t stream) {
     if (T <= 0 || H <= 0) return 0;
     const dim3 grid(T, (H + 3) / 4), block(128);
-#define HNG(TA, TW) head_norm_gate_kernel<TA, TW><<<grid, block, 0, stream>>>(o, (const TA*)g, g_stride, (const TW*)w, (TA*)out, H, dv, eps, act)
+#define HNG(TA, TW) launch_after_wait(head_norm_gate_kernel<TA, TW>, grid, block, 0, stream, o, (const TA*)g, g_stride, (const TW*)w, (TA*)out, H, dv, eps, act)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) HNG(float, float); else HNG(float, bf16); }
     else { if (w_dtype == TL_F32) HNG(bf16, float); else HNG(bf16, bf16); }
 #undef HNG
@@ -430,6 +433,8 @@ __global__ void sum_normed_kernel(const TA* __restrict__ a, const TA* __restrict
                                   const TW* __restrict__ wb, TA* __restrict__ out, int W, float eps, float c) {
     __shared__ float red[33];
     const size_t base = (size_t)blockIdx.x * W;
+    grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
+    grid_dependency_trigger();
     float sa = 0.f, sb = 0.f;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         const float x = to_f<TA>(a[base + i]), y = to_f<TA>(b[base + i]);
@@ -447,7 +452,7 @@ __global__ void sum_normed_kernel(const TA* __restrict__ a, const TA* __restrict
 TL_EXPORT int tl_sum_normed(const void* a, const void* b, const void* wa, const void* wb, int w_dtype, void* out,
                             int act_dtype, int T, int W, float eps, float c, cudaStream_t stream) {
     if (T <= 0) return 0;
-#define SN(TA, TW) sum_normed_kernel<TA, TW><<<T, 256, 0, stream>>>((const TA*)a, (const TA*)b, (const TW*)wa, (const TW*)wb, (TA*)out, W, eps, c)
+#define SN(TA, TW) launch_after_wait(sum_normed_kernel<TA, TW>, dim3(T), dim3(256), 0, stream, (const TA*)a, (const TA*)b, (const TW*)wa, (const TW*)wb, (TA*)out, W, eps, c)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) SN(float, float); else SN(float, bf16); }
     else { if (w_dtype == TL_F32) SN(bf16, float); else SN(bf16, bf16); }
 #undef SN

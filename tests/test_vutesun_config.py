@@ -63,3 +63,15 @@ def test_a_wrong_configuration_names_its_key(edit, word):
     edit(raw)
     with pytest.raises(ConfigError, match=word):
         VutesunConfig.from_dict(raw)
+
+
+def test_the_command_writes_random_weights_for_the_design(tmp_path):
+    from tensorline_b200 import cli
+    from tensorline_b200.weights import load_weights
+    (tmp_path / "c.json").write_text(json.dumps(V2))
+    out = tmp_path / "model"
+    assert cli.main(["random-weights", "--config", str(tmp_path / "c.json"), "--out", str(out), "--seed", "1"]) == 0
+    assert json.loads((out / "config.json").read_text()) == V2
+    cfg = VutesunConfig.from_dict(V2)
+    w = load_weights(out, expected_tensors(cfg))             # every tensor the model expects, nothing else
+    assert w["l0.mix.left.sink"].shape == (4,) and "l1.norm2" not in w and w["l2.mlp.e1.up"].shape == (16, 72)

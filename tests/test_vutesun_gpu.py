@@ -457,3 +457,14 @@ def test_further_shapes_of_the_design(name, dtype, tmp_path):
     check(m, dtype, cut, "changing portions")
     if dtype == "float32":
         assert all(torch.equal(cut[k], whole[k]) for k in whole)
+
+
+def test_generate_from_the_command_line(model, capsys):
+    """The `tensorline` command with token ids, 32-bit, against greedy decoding with the plain model."""
+    from tensorline_b200 import cli
+    assert cli.main(["--model", str(model["folder"]), "--dtype", "float32", "--prompt-ids", "5,9,40,17", "--prompt-ids", "7",
+                     "--max-tokens", "5", "--ignore-eos", "--block-size", str(model["page"]), "--num-blocks", "16",
+                     "--max-num-seqs", "4", "--max-model-len", "64"]) == 0
+    import json
+    lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert [l["token_ids"] for l in lines] == [greedy_generate(model["plain"], [5, 9, 40, 17], 5), greedy_generate(model["plain"], [7], 5)]
