@@ -20,7 +20,7 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_feed_forward
-from .linear import matmul, resolve
+from .linear import resolve
 
 # up to this many tokens a step the experts are streamed pair by pair
 STREAM_MAX_TOKENS = int(os.environ.get("TENSORLINE_B200_MOE_STREAM_MAX_TOKENS", 32))

@@ -4,7 +4,6 @@ with the last tokens one by one, in portions down to two tokens, and mixed in a 
 slots are used again; decoding from CUDA graphs; greedy generation through `Engine.generate` and the scheduler.
 In 32-bit every schedule must give the same bits: a difference under one schedule only is a fault of the cache,
 the state or the batch."""
-import math
 
 import pytest
 import torch
