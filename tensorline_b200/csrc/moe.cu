@@ -83,15 +83,19 @@ template <> __device__ __forceinline__ void warp_dot4<bf16>(const bf16* __restri
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) small_proj_kernel(const TA* __restrict__ h, int ldh, const TW* __restrict__ w,
                                                          const TW* __restrict__ bias, float* __restrict__ out, int ldo, int N, int K) {
-    extern __shared__ float xs[];
+    extern __shared__ __align__(16) float xs[];
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
     grid_dependency_trigger();
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * ldh + k]);
     __syncthreads();
-    for (int n = blockIdx.y * 4 + wid; n < N; n += gridDim.y * 4) {      // an output a warp
-        const float v = warp_dot<TW>(w + (size_t)n * K, xs, K, lane);
-        if (lane == 0) out[(size_t)t * ldo + n] = v + (bias ? to_f<TW>(bias[n]) : 0.f);
+    for (int n = (blockIdx.y * 4 + wid) * 4; n < N; n += gridDim.y * 16) {      // four outputs a warp, their loads in flight together
+        float v[4];
+        const int rows = min(4, N - n);
+        warp_dot4<TW>(w + (size_t)n * K, K, rows, xs, K, lane, v);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (lane == 0 && r < rows) out[(size_t)t * ldo + n + r] = v[r] + (bias ? to_f<TW>(bias[n + r]) : 0.f);
     }
 }
 
@@ -101,7 +105,7 @@ TL_EXPORT int tl_small_proj(const void* h, int act_dtype, int ldh, const void* w
     const size_t smem = (size_t)K * sizeof(float);
     if (smem > 48 * 1024) return 1;
     // few tokens: the outputs of a token are dealt out to several blocks, so that a step of one token still fills SMs
-    const dim3 grid(T, T >= 512 ? 1 : min((N + 3) / 4, 64));
+    const dim3 grid(T, T >= 512 ? 1 : min((N + 15) / 16, 64));
 #define SP(TA, TW) launch_after_wait(small_proj_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, ldh, (const TW*)w, (const TW*)bias, out, ldo, N, K)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) SP(float, float); else SP(float, bf16); }
     else { if (w_dtype == TL_F32) SP(bf16, float); else SP(bf16, bf16); }
@@ -158,7 +162,7 @@ constexpr int MOE_DOWN_ROWS = 4;                         // output rows a block 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, const TW* __restrict__ w_up, const int* __restrict__ idx,
                                                      TA* __restrict__ a, int K, int F, int top) {
-    extern __shared__ float xs[];
+    extern __shared__ __align__(16) float xs[];
     const int pair = blockIdx.x, t = pair / top, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
     grid_dependency_trigger();
