@@ -390,9 +390,10 @@ TL_EXPORT int tl_linear_scan(const void* proj, int act_dtype, int stride, int q_
 
 // ------------------------------------------------------------------ per-head RMS norm, weight, gate
 // out[t, h, j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * (w ? w[h dv + j] : 1) * act(g[t, h dv + j]); one warp per
-// (token, head); act 0: no gate, 1: sigmoid, 2: silu.  o is float, g and out of the activation type.
-template <typename TA, typename TW>
-__global__ void head_norm_gate_kernel(const float* __restrict__ o, const TA* __restrict__ g, int g_stride,
+// (token, head); act 0: no gate, 1: sigmoid, 2: silu.  o is float, out of the activation type, g of its own type (the
+// projection that holds the gate may be kept in float).
+template <typename TA, typename TW, typename TG>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const TG* __restrict__ g, int g_stride,
                                       const TW* __restrict__ w, TA* __restrict__ out, int H, int dv, float eps, int act) {
     const int t = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
@@ -407,7 +408,7 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const TA* __r
         float v = row[j] * rstd;
         if (w) v *= to_f<TW>(w[h * dv + j]);
         if (act) {
-            const float x = to_f<TA>(g[(size_t)t * g_stride + h * dv + j]);
+            const float x = to_f<TG>(g[(size_t)t * g_stride + h * dv + j]);
             const float s = 1.0f / (1.0f + expf(-x));
             v *= act == 1 ? s : x * s;
         }
@@ -415,13 +416,15 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const TA* __r
     }
 }
 
-TL_EXPORT int tl_head_norm_gate(const float* o, const void* g, int g_stride, const void* w, int w_dtype, void* out,
+TL_EXPORT int tl_head_norm_gate(const float* o, const void* g, int g_dtype, int g_stride, const void* w, int w_dtype, void* out,
                                 int act_dtype, int T, int H, int dv, float eps, int act, cudaStream_t stream) {
     if (T <= 0 || H <= 0) return 0;
     const dim3 grid(T, (H + 3) / 4), block(128);
-#define HNG(TA, TW) launch_after_wait(head_norm_gate_kernel<TA, TW>, grid, block, 0, stream, o, (const TA*)g, g_stride, (const TW*)w, (TA*)out, H, dv, eps, act)
-    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) HNG(float, float); else HNG(float, bf16); }
-    else { if (w_dtype == TL_F32) HNG(bf16, float); else HNG(bf16, bf16); }
+#define HNG(TA, TW, TG) launch_after_wait(head_norm_gate_kernel<TA, TW, TG>, grid, block, 0, stream, o, (const TG*)g, g_stride, (const TW*)w, (TA*)out, H, dv, eps, act)
+#define HNG_G(TA, TW) { if (g_dtype == TL_F32) HNG(TA, TW, float); else HNG(TA, TW, bf16); }
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) HNG_G(float, float) else HNG_G(float, bf16) }
+    else { if (w_dtype == TL_F32) HNG_G(bf16, float) else HNG_G(bf16, bf16) }
+#undef HNG_G
 #undef HNG
     return tl_launch_status();
 }

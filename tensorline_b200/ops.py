@@ -31,7 +31,7 @@ _SIGNATURES = {
                        _I, _I, _F, _I, _P],
     "tl_scan_state_floats": [_I, _I],
     "tl_scan_columns": [],
-    "tl_head_norm_gate": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
+    "tl_head_norm_gate": [_P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
     "tl_sum_normed": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _F, _P],
     "tl_small_proj": [_P, _I, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "tl_topk_softmax": [_P, _I, _I, _P, _P, _I, _P],
@@ -475,21 +475,22 @@ _ACTS = {None: 0, "sigmoid": 1, "silu": 2}
 def head_norm_gate(o: torch.Tensor, out: torch.Tensor, H: int, dv: int, eps: float, weight: torch.Tensor | None = None,
                    gate: torch.Tensor | None = None, gate_off: int = 0, act: str | None = None) -> None:
     """out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[h, :] * act(gate[t, gate_off + h dv + :]); o float32
-    [T, H dv], out and gate rows of the activation type; weight (any float type, [H dv]) and the gate are optional."""
+    [T, H dv], out of the activation type, the gate rows float32 or bfloat16; weight (any float type, [H dv]) and the gate
+    are optional."""
     T = o.shape[0]
     if o.dtype != torch.float32 or o.shape != (T, H * dv) or out.shape != o.shape:
         raise KernelError("head_norm_gate: o must be float32 [T, H dv] and out of its shape")
     if act not in _ACTS or (act is not None) != (gate is not None):
         raise KernelError("head_norm_gate: a gate comes with 'sigmoid' or 'silu'")
     _contig(o, "o"); _contig(out, "out")
-    g_ptr, g_stride = None, 0
+    g_ptr, g_stride, g_code = None, 0, 0
     if gate is not None:
-        if gate.dtype != out.dtype or gate.stride(1) != 1 or gate_off + H * dv > gate.shape[1]:
-            raise KernelError("head_norm_gate: the gate rows must be of out's type and hold H dv columns from gate_off")
-        g_ptr, g_stride = _ptr(gate) + gate_off * gate.element_size(), gate.stride(0)
+        if gate.stride(1) != 1 or gate_off + H * dv > gate.shape[1]:
+            raise KernelError("head_norm_gate: the gate rows must hold H dv columns from gate_off")
+        g_ptr, g_stride, g_code = _ptr(gate) + gate_off * gate.element_size(), gate.stride(0), dtype_code(gate.dtype)
     if weight is not None and (weight.numel() != H * dv or not weight.is_contiguous()):
         raise KernelError("head_norm_gate: weight must be [H dv]")
-    _check(core().tl_head_norm_gate(_ptr(o), g_ptr, g_stride, _ptr(weight), dtype_code(weight.dtype) if weight is not None else 0,
+    _check(core().tl_head_norm_gate(_ptr(o), g_ptr, g_code, g_stride, _ptr(weight), dtype_code(weight.dtype) if weight is not None else 0,
                                     _ptr(out), dtype_code(out.dtype), T, H, dv, float(eps), _ACTS[act], _stream()), "head_norm_gate")
 
 

@@ -15,7 +15,7 @@ from .. import ops
 def attend(mixer, qkv, o, ctx, cache, table, rope=None) -> None:
     nq, nkv, d = mixer.nq, mixer.nkv, mixer.d
     sink = getattr(mixer, "sink", None)
-    if qkv.dtype == torch.float32 or ctx.force_exact_attention:
+    if qkv.dtype == torch.float32 or ctx.force_exact_attention or d > 256:     # heads wider than the tensor-core kernels take
         ops.attn_tokenwise(qkv, qkv.shape[1], o, cache.k, cache.v, table, ctx.page_size, ctx.pos, ctx.req_slot,
                            nq, nkv, d, mixer.window, mixer.scale, sink=sink)
         return

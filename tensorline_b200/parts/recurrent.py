@@ -17,7 +17,8 @@ gate, the output projection):
 
 The state lives in the request's state slot (`SlotState`), in float32, zero for a new request (which is also
 m_0 = 0), in the scan kernel's own layout; the gates' pre-activations, the rotation, the exponentials and the
-norms are float32 in both engines, q, k, v and g are what the stacked projection leaves in the activation type.
+norms are float32 in both engines, and q, k, v and g are the stacked projection's float32 results (bfloat16 inputs and
+weights in the bfloat16 engine, accumulated and kept in float32).
 The mixers read the step from device tensors only, so steps of single tokens are captured in CUDA graphs.
 """
 from __future__ import annotations
@@ -88,10 +89,13 @@ class _MatrixState(Part):
     def forward(self, h, ctx, cache):
         H, d, dv = self.H, self.d, self.dv
         T = h.shape[0]
-        proj = resolve(matmul(h, self.w_in))
+        # q, k, v and g stay as the product accumulated them, in float32: what enters the recurrence is not rounded again
+        # (rounding q and k to bfloat16 alone moved the logits of a small model by several per cent where n . q or
+        # S^T q nearly cancel)
+        proj = resolve(matmul(h, self.w_in, out_dtype=torch.float32))
         o = torch.empty((T, H * dv), dtype=torch.float32, device=h.device)
         self._scan(h, proj, ctx, cache.state, o)
-        y = torch.empty((T, H * dv), dtype=proj.dtype, device=h.device)
+        y = torch.empty((T, H * dv), dtype=h.dtype, device=h.device)
         ops.head_norm_gate(o, y, H, dv, self.eps, weight=self._head_weight(), gate=proj, gate_off=2 * H * d + H * dv,
                            act=self.gate_act)
         return matmul(y, self.w_o)

@@ -154,12 +154,14 @@ def test_linear_scan_keeps_a_far_token():
 
 
 @pytest.mark.parametrize("adt", DT)
+@pytest.mark.parametrize("gdt", DT)
 @pytest.mark.parametrize("act,weighted", [("sigmoid", True), ("silu", False), (None, True)])
-def test_head_norm_gate(adt, act, weighted):
+def test_head_norm_gate(adt, gdt, act, weighted):
+    """The gate rows may be float32 beside a bfloat16 output (a projection kept as it was accumulated)."""
     from tensorline_b200 import ops
     T, H, dv, eps = 9, 3, 40, 1e-5
     o = rnd(T, H * dv, seed=1, scale=3.0)
-    gate = rnd(T, 7 + H * dv, seed=2, dtype=adt)
+    gate = rnd(T, 7 + H * dv, seed=2, dtype=gdt)
     w = rnd(H * dv, seed=3, dtype=torch.bfloat16) + 1 if weighted else None
     out = torch.zeros(T, H * dv, dtype=adt, device="cuda")
     ops.head_norm_gate(o.cuda(), out, H, dv, eps, weight=w.cuda() if weighted else None,
