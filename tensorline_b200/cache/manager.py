@@ -35,10 +35,12 @@ from .pages import CacheError, PagePool, page_hash
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of `num_kv_heads` heads of `head_dim`, all of them (`window` None) or
-    the last `window` positions."""
+    the last `window` positions.  `shared_values`: the value of a token is its key row itself (a mixer that
+    caches one latent vector a token): one page tensor serves as both."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    shared_values: bool = False
 
     @property
     def group_key(self):

@@ -171,6 +171,20 @@ struct TlTraceHost {
 // same bits; the 32-bit engine divides exactly.
 __device__ __forceinline__ float tl_silu_mul(float g, float u) { return __fdividef(g, 1.0f + expf(-g)) * u; }
 
+// Activation codes of the C interface, and the tanh form of gelu: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+#define TL_ACT_SILU 0
+#define TL_ACT_GELU_TANH 1
+#define TL_ACT_RELU_SQUARED 2
+__device__ __forceinline__ float tl_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// act(g) for the codes above, exact arithmetic (the 32-bit engine and every float-accumulating kernel)
+__device__ __forceinline__ float tl_act(float g, int act) {
+    if (act == TL_ACT_GELU_TANH) return tl_gelu_tanh(g);
+    if (act == TL_ACT_RELU_SQUARED) { const float r = fmaxf(g, 0.f); return r * r; }
+    return g / (1.0f + expf(-g));
+}
+
 // Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while
 // the kernel before it in the stream is still running; its blocks run their set-up and then stop in
 // grid_dependency_wait() until that kernel has finished and its writes are visible.  Every kernel launched

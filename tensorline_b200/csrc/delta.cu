@@ -1,0 +1,235 @@
+// The gated delta rule: a matrix memory per head that is decayed, corrected towards the new value and read, token by token.
+//
+//   S <- g_t S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t          S: [d, dv] per (request, head), float
+//   beta_t = sigmoid(b_t),   g_t = exp(-exp(A_log) softplus(a_t + dt_bias))                 b_t, a_t: two small projections
+//
+// q, k, v first pass a short causal convolution over time per channel and silu; q and k are then scaled to unit length per
+// head (x / sqrt(sum x^2 + unit_eps)), q also by q_scale.  Several value heads may share a q/k head.  Three kernels:
+//   conv_prep     convolution (the `taps - 1` inputs before the step come from the request's slot), silu, unit length
+//   conv_keep     the slot's last `taps - 1` inputs after the step
+//   delta_scan    the recurrence; a thread owns R consecutive rows of one value column of S in registers, IS threads a
+//                 column, 16 columns a block; the two column sums a token needs are finished by shuffles.
+// Everything is float: the convolution's sums, the unit norms, gates, decays and the state.  The sequence of operations on a
+// state element and on an output does not depend on where a step was cut.
+#include "common.cuh"
+
+constexpr int DELTA_JS = 16;     // value columns a block
+constexpr int DELTA_C = 16;      // tokens a chunk
+constexpr int DELTA_TOK = 16;    // tokens a block of conv_prep
+
+// ------------------------------------------------------------------ convolution + silu + unit length
+// grid (requests, chunks of DELTA_TOK tokens); a warp a (token, unit), unit = a head of q, k or v.  Output float [T, C].
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(128) conv_prep_kernel(const TA* __restrict__ proj, int stride, const TW* __restrict__ taps_w, int taps,
+                                                        const float* __restrict__ conv_state, long long slot_stride,
+                                                        const int* __restrict__ q_start, const int* __restrict__ slots,
+                                                        float* __restrict__ out, int C, int nqk, int d, int nv, int dv,
+                                                        float unit_eps, float q_scale) {
+    const int b = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    const int c0 = t0 + blockIdx.y * DELTA_TOK, c1 = min(t1, c0 + DELTA_TOK);
+    if (c0 >= t1) return;
+    const float* st = conv_state + (size_t)slots[b] * slot_stride;       // [taps - 1][C], oldest first
+    const int units = 2 * nqk + nv;
+    for (int item = wid; item < (c1 - c0) * units; item += 4) {
+        const int t = c0 + item / units, u = item % units;
+        const bool qk = u < 2 * nqk;
+        const int width = qk ? d : dv, base = qk ? u * d : 2 * nqk * d + (u - 2 * nqk) * dv;
+        const int i = t - t0;                                            // the token's place in the step
+        float ss = 0.f;
+        for (int e = lane; e < width; e += 32) {
+            const int c = base + e;
+            float acc = 0.f;
+            for (int j = 0; j < taps; ++j) {                             // tap j reads the input taps - 1 - j tokens back
+                const int back = taps - 1 - j, src = i - back;
+                const float xin = src >= 0 ? to_f<TA>(proj[(size_t)(t0 + src) * stride + c])
+                                           : st[(size_t)(taps - 1 + src) * C + c];
+                acc = fmaf(to_f<TW>(taps_w[(size_t)c * taps + j]), xin, acc);
+            }
+            const float y = acc / (1.0f + expf(-acc));
+            out[(size_t)t * C + c] = y;
+            ss = fmaf(y, y, ss);
+        }
+        if (qk) {
+            ss = warp_sum(ss);
+            const float r = (1.0f / sqrtf(ss + unit_eps)) * (u < nqk ? q_scale : 1.0f);
+            __syncwarp();
+            for (int e = lane; e < width; e += 32) out[(size_t)t * C + base + e] *= r;
+        }
+    }
+}
+
+// The slot's inputs after the step: the last taps - 1 of (what the slot held, then the step's inputs).  A thread a channel;
+// going from the oldest place on, every place reads a place behind it or the step's rows, so nothing is read after it
+// was overwritten.
+template <typename TA>
+__global__ void conv_keep_kernel(const TA* __restrict__ proj, int stride, int taps, float* __restrict__ conv_state, long long slot_stride,
+                                 const int* __restrict__ q_start, const int* __restrict__ slots, int C) {
+    const int b = blockIdx.x;
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const int t0 = q_start[b], n = q_start[b + 1] - t0;
+    if (n <= 0) return;
+    float* st = conv_state + (size_t)slots[b] * slot_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        for (int j = 0; j < taps - 1; ++j) {
+            const int src = n - (taps - 1) + j;                          // place in the step; negative: still the slot's
+            st[(size_t)j * C + c] = src >= 0 ? to_f<TA>(proj[(size_t)(t0 + src) * stride + c]) : st[(size_t)(j + n) * C + c];
+        }
+    }
+}
+
+TL_EXPORT int tl_conv_prep(const void* proj, int act_dtype, int stride, const void* taps_w, int w_dtype, int taps, float* conv_state,
+                           long long slot_stride, const int* q_start, const int* slots, float* out, int B, int max_q_len,
+                           int nqk, int d, int nv, int dv, float unit_eps, float q_scale, cudaStream_t stream) {
+    if (B <= 0 || max_q_len <= 0) return 0;
+    if (taps < 1 || (taps > 1 && !conv_state)) return 1;
+    const int C = 2 * nqk * d + nv * dv;
+    const dim3 grid(B, (max_q_len + DELTA_TOK - 1) / DELTA_TOK);
+    if (grid.y > 65535) return 1;
+#define CP(TA, TW) launch_after_wait(conv_prep_kernel<TA, TW>, grid, dim3(128), 0, stream, (const TA*)proj, stride, (const TW*)taps_w, taps, \
+        (const float*)conv_state, slot_stride, q_start, slots, out, C, nqk, d, nv, dv, unit_eps, q_scale)
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) CP(float, float); else CP(float, bf16); }
+    else { if (w_dtype == TL_F32) CP(bf16, float); else CP(bf16, bf16); }
+#undef CP
+    int e = tl_launch_status();
+    if (e || taps == 1) return e;
+    const dim3 kgrid(B, (C + 255) / 256 < 64 ? (C + 255) / 256 : 64);
+    if (act_dtype == TL_F32) launch_after_wait(conv_keep_kernel<float>, kgrid, dim3(256), 0, stream, (const float*)proj, stride, taps, conv_state, slot_stride, q_start, slots, C);
+    else launch_after_wait(conv_keep_kernel<bf16>, kgrid, dim3(256), 0, stream, (const bf16*)proj, stride, taps, conv_state, slot_stride, q_start, slots, C);
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ the recurrence
+struct DeltaArgs {
+    const float* qkv; int stride;          // [T, stride] float: q [nqk, d], k [nqk, d], v [H, dv] as conv_prep left them
+    int q_off, k_off, v_off;
+    const float* gates; int gate_stride;   // [T, >= 2 H]: b_t (beta's pre-activation) then a_t (the decay's), per head
+    const float* A_log; const float* dt_bias;      // [H]
+    float* state; long long slot_stride;
+    const int* q_start; const int* slots;
+    float* out;                            // [T, H * dv]
+    int H, nqk, d, dv;
+};
+
+template <int R, int IS> struct DeltaShape {
+    static constexpr int NT = IS * DELTA_JS;
+    static constexpr int PB = R * NT;                            // floats of state a (head, column slice)
+    static constexpr int RS = R + 4;                             // padded: the IS threads of a column read different banks
+    static constexpr int TS = IS * RS;
+    static constexpr int CH = IS >= 32 ? DELTA_C / 2 : DELTA_C;  // tokens a chunk: q and k of a chunk stay under 48 KB
+};
+
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+template <int R, int IS>
+__global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const DeltaArgs A) {
+    using Sh = DeltaShape<R, IS>;
+    constexpr int NT = Sh::NT, PB = Sh::PB, RS = Sh::RS, TS = Sh::TS, CH = Sh::CH;
+    __shared__ __align__(16) float qs[CH * TS];
+    __shared__ __align__(16) float ks[CH * TS];
+    __shared__ float vs[CH * DELTA_JS];
+    __shared__ float gg[CH], gb[CH];
+    const int d = A.d;
+    const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+    const int hq = h / (A.H / A.nqk);                            // the q/k head this value head reads
+    const int tid = threadIdx.x, islice = tid % IS, j = tid / IS;
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const int t0 = A.q_start[b], t1 = A.q_start[b + 1];
+    if (t0 >= t1) return;
+    float* st = A.state + (size_t)A.slots[b] * A.slot_stride + ((size_t)h * gridDim.z + z) * PB;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) S[r] = st[r * NT + tid];
+    const int jcol = z * DELTA_JS + j;
+    const bool live = jcol < A.dv;
+    const float neg_rate = -expf(A.A_log[h]), bias = A.dt_bias[h];
+    for (int i = tid; i < CH * TS; i += NT) { qs[i] = 0.f; ks[i] = 0.f; }     // rows beyond d stay zero
+    __syncthreads();
+    for (int c0 = t0; c0 < t1; c0 += CH) {
+        const int n = min(CH, t1 - c0);
+        for (int i = tid; i < n * d; i += NT) {
+            const int t = i / d, e = i - t * d;
+            const float* row = A.qkv + (size_t)(c0 + t) * A.stride + hq * d + e;
+            qs[t * TS + (e / R) * RS + (e % R)] = row[A.q_off];
+            ks[t * TS + (e / R) * RS + (e % R)] = row[A.k_off];
+        }
+        for (int i = tid; i < n * DELTA_JS; i += NT) {
+            const int t = i / DELTA_JS, col = z * DELTA_JS + (i - t * DELTA_JS);
+            vs[i] = col < A.dv ? A.qkv[(size_t)(c0 + t) * A.stride + A.v_off + h * A.dv + col] : 0.f;
+        }
+        if (tid < n) {
+            const float* g = A.gates + (size_t)(c0 + tid) * A.gate_stride;
+            gb[tid] = 1.0f / (1.0f + expf(-g[h]));
+            gg[tid] = expf(neg_rate * softplus_f(g[A.H + h] + bias));
+        }
+        __syncthreads();
+        const float* kt = ks + islice * RS;
+        const float* qt = qs + islice * RS;
+        for (int t = 0; t < n; ++t) {
+            const float g = gg[t];
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; r += 4) {
+                const float4 kk = *reinterpret_cast<const float4*>(kt + t * TS + r);
+                S[r] *= g;     acc = fmaf(S[r], kk.x, acc);
+                S[r + 1] *= g; acc = fmaf(S[r + 1], kk.y, acc);
+                S[r + 2] *= g; acc = fmaf(S[r + 2], kk.z, acc);
+                S[r + 3] *= g; acc = fmaf(S[r + 3], kk.w, acc);
+            }
+#pragma unroll
+            for (int o = 1; o < IS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            const float u = gb[t] * (vs[t * DELTA_JS + j] - acc);
+            float rd = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; r += 4) {
+                const float4 kk = *reinterpret_cast<const float4*>(kt + t * TS + r);
+                const float4 qq = *reinterpret_cast<const float4*>(qt + t * TS + r);
+                S[r] = fmaf(kk.x, u, S[r]);         rd = fmaf(S[r], qq.x, rd);
+                S[r + 1] = fmaf(kk.y, u, S[r + 1]); rd = fmaf(S[r + 1], qq.y, rd);
+                S[r + 2] = fmaf(kk.z, u, S[r + 2]); rd = fmaf(S[r + 2], qq.z, rd);
+                S[r + 3] = fmaf(kk.w, u, S[r + 3]); rd = fmaf(S[r + 3], qq.w, rd);
+            }
+#pragma unroll
+            for (int o = 1; o < IS; o <<= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
+            if (live && islice == 0) A.out[(size_t)(c0 + t) * A.H * A.dv + (size_t)h * A.dv + jcol] = rd;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) st[r * NT + tid] = S[r];
+}
+
+// How a head of d rows is dealt out: 0: R 4 x IS 8 (d <= 32), 1: 8 x 8 (<= 64), 2: 8 x 16 (<= 128), 3: 8 x 32 (<= 256); -1: too large.
+static int delta_shape(int d) { return d <= 32 ? 0 : d <= 64 ? 1 : d <= 128 ? 2 : d <= 256 ? 3 : -1; }
+
+TL_EXPORT int tl_delta_state_floats(int d) {
+    switch (delta_shape(d)) {
+        case 0: return DeltaShape<4, 8>::PB;
+        case 1: return DeltaShape<8, 8>::PB;
+        case 2: return DeltaShape<8, 16>::PB;
+        case 3: return DeltaShape<8, 32>::PB;
+    }
+    return 0;
+}
+TL_EXPORT int tl_delta_columns() { return DELTA_JS; }
+
+TL_EXPORT int tl_delta_scan(const float* qkv, int stride, int q_off, int k_off, int v_off, const float* gates, int gate_stride,
+                            const float* A_log, const float* dt_bias, float* state, long long slot_stride, const int* q_start,
+                            const int* slots, float* out, int B, int H, int nqk, int d, int dv, cudaStream_t stream) {
+    if (B <= 0 || H <= 0) return 0;
+    if (H > 65535 || nqk < 1 || H % nqk) return 1;
+    const DeltaArgs A{qkv, stride, q_off, k_off, v_off, gates, gate_stride, A_log, dt_bias, state, slot_stride, q_start, slots, out,
+                      H, nqk, d, dv};
+    const dim3 grid(B, H, (dv + DELTA_JS - 1) / DELTA_JS);
+    switch (delta_shape(d)) {
+        case 0: return launch_after_wait(delta_scan_kernel<4, 8>, grid, dim3(DeltaShape<4, 8>::NT), 0, stream, A);
+        case 1: return launch_after_wait(delta_scan_kernel<8, 8>, grid, dim3(DeltaShape<8, 8>::NT), 0, stream, A);
+        case 2: return launch_after_wait(delta_scan_kernel<8, 16>, grid, dim3(DeltaShape<8, 16>::NT), 0, stream, A);
+        case 3: return launch_after_wait(delta_scan_kernel<8, 32>, grid, dim3(DeltaShape<8, 32>::NT), 0, stream, A);
+    }
+    return 1;
+}

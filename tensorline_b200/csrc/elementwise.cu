@@ -216,8 +216,9 @@ TL_EXPORT int tl_add_rmsnorm(void* x, const void* r, const void* w, int w_dtype,
 // gu is [T, 2*I], out [T, I].  Gate and up columns alternate in blocks of `blk` columns: out column c has its
 // gate at (c / blk) * 2 blk + c % blk and its up value blk columns further.  blk = I is the plain layout
 // (gate in [0, I), up in [I, 2I)); blk = 64 is what a product against interleaved weight rows leaves.
+// `act` picks the gate's function: TL_ACT_SILU, or TL_ACT_GELU_TANH (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).
 template <typename TA>
-__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, int blk, size_t total) {
+__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, int blk, size_t total, int act) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
@@ -225,7 +226,8 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
         const int gc = (c / blk) * 2 * blk + c % blk;
         const float g = to_f<TA>(gu[t * 2 * I + gc]);
         const float u = to_f<TA>(gu[t * 2 * I + gc + blk]);
-        if constexpr (sizeof(TA) == 4) out[idx] = (g / (1.0f + expf(-g))) * u;     // the 32-bit engine: exact division
+        if (act == TL_ACT_GELU_TANH) out[idx] = from_f<TA>(tl_gelu_tanh(g) * u);
+        else if constexpr (sizeof(TA) == 4) out[idx] = (g / (1.0f + expf(-g))) * u;     // the 32-bit engine: exact division
         else                           out[idx] = from_f<TA>(tl_silu_mul(g, u));
     }
 }
@@ -233,7 +235,7 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
 // 8 values (16 bytes of bfloat16) per thread and chunk: requires I % 8 == 0 and blk % 8 == 0.  grid (column
 // groups, tokens): no division per element; with many tokens a thread takes two chunks a block's width apart,
 // so four 16-byte loads are in flight before the first is used; with few it takes one, for more blocks.
-template <int CHUNKS>
+template <int CHUNKS, int ACT>
 __global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, int blk) {
     const size_t t = blockIdx.y;
     const int c0 = (blockIdx.x * 256 * CHUNKS + threadIdx.x) * 8;
@@ -263,29 +265,86 @@ __global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restri
         for (int e = 0; e < 4; ++e) {
             const float g0 = __low2float(g2[e]), g1 = __high2float(g2[e]);
             const float u0 = __low2float(u2[e]), u1 = __high2float(u2[e]);
-            o2[e] = __floats2bfloat162_rn(tl_silu_mul(g0, u0), tl_silu_mul(g1, u1));
+            if (ACT == TL_ACT_GELU_TANH) o2[e] = __floats2bfloat162_rn(tl_gelu_tanh(g0) * u0, tl_gelu_tanh(g1) * u1);
+            else o2[e] = __floats2bfloat162_rn(tl_silu_mul(g0, u0), tl_silu_mul(g1, u1));
         }
         *reinterpret_cast<uint4*>(out + t * I + cs[k]) = ov;
     }
 }
 
-TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I, int blk, cudaStream_t stream) {
+TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I, int blk, int act, cudaStream_t stream) {
     const size_t total = (size_t)T * I;
     if (total == 0) return 0;
-    if (blk <= 0 || I % blk) return 1;
+    if (blk <= 0 || I % blk || (act != TL_ACT_SILU && act != TL_ACT_GELU_TANH)) return 1;
     const int threads = 256;
     if (act_dtype == TL_BF16 && (I & 7) == 0 && (blk & 7) == 0 && T <= 65535 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
-        if (T >= 256)
-            return launch_after_wait(silu_mul_vec8_kernel<2>, dim3((unsigned)((I / 8 + 511) / 512), (unsigned)T), dim3(threads), 0, stream,
-                                     (const bf16*)gu, (bf16*)out, I, blk);
-        return launch_after_wait(silu_mul_vec8_kernel<1>, dim3((unsigned)((I / 8 + 255) / 256), (unsigned)T), dim3(threads), 0, stream,
-                                 (const bf16*)gu, (bf16*)out, I, blk);
+#define SMV(CH, A) launch_after_wait(silu_mul_vec8_kernel<CH, A>, dim3((unsigned)((I / 8 + 256 * CH - 1) / (256 * CH)), (unsigned)T), dim3(threads), 0, stream, \
+                                 (const bf16*)gu, (bf16*)out, I, blk)
+        if (act == TL_ACT_GELU_TANH) return T >= 256 ? SMV(2, TL_ACT_GELU_TANH) : SMV(1, TL_ACT_GELU_TANH);
+        return T >= 256 ? SMV(2, TL_ACT_SILU) : SMV(1, TL_ACT_SILU);
+#undef SMV
     }
     const size_t cap = (size_t)tl_num_sms() * 16;
     const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
     if (act_dtype == TL_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, blk, total);
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, blk, total, act);
     else
-        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, blk, total);
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, blk, total, act);
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ a sub-block's own norm, the residual sum, the next norm
+// For blocks that normalise a sub-block's output before it joins the residual stream:
+//   x += a / rms(a) * w_post  (+ extra, a row vector added once);   h = x / rms(x) * w_pre
+// all in float, one block a row.  `a` null: no addend (only extra and the norm); `out` null: no norm (only the sum);
+// `rows`: as above, x is then left alone.  Nothing is rounded before h.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256) post_norm_add_norm_kernel(float* __restrict__ x, const TA* __restrict__ a, const TW* __restrict__ w_post,
+                                                                 const float* __restrict__ extra, const TW* __restrict__ w_pre,
+                                                                 TA* __restrict__ out, const int* __restrict__ rows, int H, float eps,
+                                                                 int write_x) {
+    __shared__ float red[33];
+    const int i = blockIdx.x;
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const size_t src = (size_t)(rows ? rows[i] : i) * H;
+    float* xr = x + src;
+    float ra = 0.f;
+    if (a) {
+        float sa = 0.f;
+        for (int c = threadIdx.x; c < H; c += blockDim.x) { const float v = to_f<TA>(a[src + c]); sa = fmaf(v, v, sa); }
+        sa = block_sum(sa, red);
+        ra = 1.0f / sqrtf(sa / (float)H + eps);
+    }
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (a) v += to_f<TA>(a[src + c]) * ra * to_f<TW>(w_post[c]);
+        if (extra) v += extra[c];
+        if (write_x) xr[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!out) return;
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (!write_x) {                                  // the same chain of operations as above
+            if (a) v += to_f<TA>(a[src + c]) * ra * to_f<TW>(w_post[c]);
+            if (extra) v += extra[c];
+        }
+        out[(size_t)i * H + c] = from_f<TA>(v * rstd * to_f<TW>(w_pre[c]));
+    }
+}
+
+TL_EXPORT int tl_post_norm_add_norm(void* x, const void* a, const void* w_post, const float* extra, const void* w_pre, int w_dtype,
+                                    void* out, int act_dtype, const int* rows, int R, int H, float eps, int write_x,
+                                    cudaStream_t stream) {
+    if (R <= 0) return 0;
+#define PN(TA, TW) launch_after_wait(post_norm_add_norm_kernel<TA, TW>, dim3(R), dim3(256), 0, stream, (float*)x, (const TA*)a, \
+        (const TW*)w_post, extra, (const TW*)w_pre, (TA*)out, rows, H, eps, write_x)
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) PN(float, float); else PN(float, bf16); }
+    else { if (w_dtype == TL_F32) PN(bf16, float); else PN(bf16, bf16); }
+#undef PN
     return tl_launch_status();
 }

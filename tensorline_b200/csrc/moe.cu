@@ -3,6 +3,10 @@
 //   z = h Wr^T + br                         float, whatever the engine's activation type (small_proj)
 //   chosen = the `top` largest z, lowest index first on a tie; weights = softmax over the chosen z only
 //   y = sum_j weight_j * Wdown[e_j] act(Wup[e_j] h),   act(u) = relu(u)^2
+// Options, all arguments: the weights as the sigmoid of each chosen logit instead of the softmax over the chosen
+// (`mode`); gated experts, Wdown (act(Wgate x) * Wup x) with gate and up rows stacked [2F, K] (`gated`, `act`); the weight
+// on the expert's input instead of its output, x = weight * h (`in_scale`; the output sum is then unweighted); and one
+// more addend a token, gate_t * extra[t] with gate_t = sigmoid of a column of the router's product (a shared expert).
 //
 // Two routes for the experts' products.  Steps of few tokens (decoding): every (token, chosen expert) pair streams its
 // expert's rows (moe_up), and every token sums its experts' down products in the order they were chosen (moe_down):
@@ -116,13 +120,13 @@ TL_EXPORT int tl_small_proj(const void* h, int act_dtype, int ldh, const void* w
 // ------------------------------------------------------------------ choice of experts
 // One warp per token.  `top` rounds of a warp-wide arg-max (largest value, lowest index on a tie); the weights are
 // the softmax over the chosen logits.  E <= 1024, top <= 32.
-__global__ void __launch_bounds__(128) topk_softmax_kernel(const float* __restrict__ z, int E, int top, int* __restrict__ idx,
-                                                           float* __restrict__ wts, int T) {
+__global__ void __launch_bounds__(128) topk_softmax_kernel(const float* __restrict__ z, int ldz, int E, int top, int* __restrict__ idx,
+                                                           float* __restrict__ wts, int T, int mode) {
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
     grid_dependency_trigger();
     if (t >= T) return;
-    const float* row = z + (size_t)t * E;
+    const float* row = z + (size_t)t * ldz;
     unsigned taken = 0;                                  // bit c: my element lane + 32 c is chosen
     float mine = 0.f, first = 0.f, sum = 0.f;            // lane j keeps the j-th chosen logit
     for (int j = 0; j < top; ++j) {
@@ -139,18 +143,18 @@ __global__ void __launch_bounds__(128) topk_softmax_kernel(const float* __restri
         }
         if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
         if (j == 0) first = best;
-        const float p = expf(best - first);
+        const float p = mode ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         sum += p;
         if (lane == j) mine = p;
         if (lane == 0) idx[(size_t)t * top + j] = bi;
     }
-    if (lane < top) wts[(size_t)t * top + lane] = mine / sum;
+    if (lane < top) wts[(size_t)t * top + lane] = mode ? mine : mine / sum;
 }
 
-TL_EXPORT int tl_topk_softmax(const float* z, int E, int top, int* idx, float* wts, int T, cudaStream_t stream) {
+TL_EXPORT int tl_topk_softmax(const float* z, int ldz, int E, int top, int* idx, float* wts, int T, int mode, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E > 1024 || top > 32 || top > E || top < 1) return 1;
-    launch_after_wait(topk_softmax_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, z, E, top, idx, wts, T);
+    launch_after_wait(topk_softmax_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, z, ldz, E, top, idx, wts, T, mode);
     return tl_launch_status();
 }
 
@@ -158,10 +162,12 @@ TL_EXPORT int tl_topk_softmax(const float* z, int E, int top, int* idx, float* w
 constexpr int MOE_ROWS = 16;                             // output rows a block of moe_up (4 a warp, their loads in flight together)
 constexpr int MOE_DOWN_ROWS = 4;                         // output rows a block of moe_down (a warp an expert)
 
-// a[pair, f] = relu(Wup[e][f, :] . h[t, :])^2, pair = t * top + j, e = idx[pair]
+// a[pair, f] = act(s Wup[e][f, :] . h[t, :]), pair = t * top + j, e = idx[pair], s = in_scale ? in_scale[pair] : 1;
+// gated: a[pair, f] = act(s Wgu[e][f, :] . h[t, :]) * (s Wgu[e][F + f, :] . h[t, :]) with an expert's matrix [2F, K].
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, const TW* __restrict__ w_up, const int* __restrict__ idx,
-                                                     TA* __restrict__ a, int K, int F, int top) {
+                                                     TA* __restrict__ a, int K, int F, int top, int gated, int act,
+                                                     const float* __restrict__ in_scale) {
     extern __shared__ __align__(16) float xs[];
     const int pair = blockIdx.x, t = pair / top, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
@@ -169,14 +175,21 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
     const int e = idx[pair];
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * K + k]);
     __syncthreads();
-    const TW* w = w_up + (size_t)e * F * K;
+    const TW* w = w_up + (size_t)e * F * K * (gated ? 2 : 1);
+    const float sc = in_scale ? in_scale[pair] : 1.0f;
     const int f0 = blockIdx.y * MOE_ROWS + wid * (MOE_ROWS / 4), f1 = min(F, f0 + MOE_ROWS / 4);    // a warp's four rows
     for (int f = f0; f < f1; f += 4) {                   // four rows at a time: their loads are in flight together
-        float u[4];
+        float u[4], g[4];
         warp_dot4<TW>(w + (size_t)f * K, K, min(4, f1 - f), xs, K, lane, u);
+        if (gated) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) g[r] = u[r];
+            warp_dot4<TW>(w + (size_t)(F + f) * K, K, min(4, f1 - f), xs, K, lane, u);
+        }
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-            if (lane == 0 && f + r < f1) { const float v = fmaxf(u[r], 0.f); a[(size_t)pair * F + f + r] = from_f<TA>(v * v); }
+            if (lane == 0 && f + r < f1)
+                a[(size_t)pair * F + f + r] = from_f<TA>(gated ? tl_act(sc * g[r], act) * (sc * u[r]) : tl_act(sc * u[r], act));
     }
 }
 
@@ -185,7 +198,8 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
 // memory of its own, and leave their four products in red[j]; then one thread a row adds them up in the order chosen.
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a, const TW* __restrict__ w_down, const int* __restrict__ idx,
-                                                       const float* __restrict__ wts, TA* __restrict__ y, int F, int N, int top) {
+                                                       const float* __restrict__ wts, TA* __restrict__ y, int F, int N, int top,
+                                                       const TA* __restrict__ extra, const float* __restrict__ extra_gate, int ldg) {
     extern __shared__ __align__(16) float xs[];          // [4 warps][F], then red [top][4]
     float* red = xs + 4 * (size_t)F;
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -206,19 +220,23 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a,
     __syncthreads();
     if (threadIdx.x < rows) {
         float acc = 0.f;
-        for (int j = 0; j < top; ++j) acc = fmaf(wts[(size_t)t * top + j], red[j * 4 + threadIdx.x], acc);
+        for (int j = 0; j < top; ++j) acc = wts ? fmaf(wts[(size_t)t * top + j], red[j * 4 + threadIdx.x], acc) : acc + red[j * 4 + threadIdx.x];
+        if (extra) {
+            const float gt = extra_gate ? 1.0f / (1.0f + expf(-extra_gate[(size_t)t * ldg])) : 1.0f;
+            acc = fmaf(gt, to_f<TA>(extra[(size_t)t * N + n0 + threadIdx.x]), acc);
+        }
         y[(size_t)t * N + n0 + threadIdx.x] = from_f<TA>(acc);
     }
 }
 
 TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dtype, const int* idx, void* a, int P, int K,
-                        int F, int top, cudaStream_t stream) {
+                        int F, int top, int gated, int act, const float* in_scale, cudaStream_t stream) {
     if (P <= 0) return 0;
     const size_t smem = (size_t)K * sizeof(float);
     if (smem > 48 * 1024) return 1;
     const dim3 grid(P, (F + MOE_ROWS - 1) / MOE_ROWS);
     if (grid.y > 65535) return 1;
-#define MU(TA, TW) launch_after_wait(moe_up_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top)
+#define MU(TA, TW) launch_after_wait(moe_up_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top, gated, act, in_scale)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MU(float, float); else MU(float, bf16); }
     else { if (w_dtype == TL_F32) MU(bf16, float); else MU(bf16, bf16); }
 #undef MU
@@ -226,13 +244,14 @@ TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dt
 }
 
 TL_EXPORT int tl_moe_down(const void* a, int act_dtype, const void* w_down, int w_dtype, const int* idx, const float* wts,
-                          void* y, int T, int F, int N, int top, cudaStream_t stream) {
+                          void* y, int T, int F, int N, int top, const void* extra, const float* extra_gate, int ldg,
+                          cudaStream_t stream) {
     if (T <= 0) return 0;
     const size_t smem = ((size_t)4 * F + (size_t)top * 4) * sizeof(float);
     if (smem > 48 * 1024) return 1;
     const dim3 grid(T, (N + MOE_DOWN_ROWS - 1) / MOE_DOWN_ROWS);
     if (grid.y > 65535) return 1;
-#define MD(TA, TW) launch_after_wait(moe_down_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top)
+#define MD(TA, TW) launch_after_wait(moe_down_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top, (const TA*)extra, extra_gate, ldg)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MD(float, float); else MD(float, bf16); }
     else { if (w_dtype == TL_F32) MD(bf16, float); else MD(bf16, bf16); }
 #undef MD
@@ -302,7 +321,7 @@ __device__ __forceinline__ size_t moe_row(int place, int expert, const int* __re
 // experts' buffer, (expert, r): the r-th place of the expert's run, or zeros behind the run's end.
 template <typename TA>
 __global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restrict__ pair_at, const int* __restrict__ offsets, int cap,
-                                  TA* __restrict__ rows, int K, int top) {
+                                  TA* __restrict__ rows, int K, int top, const float* __restrict__ scale) {
     int place = blockIdx.x;
     if (cap) {
         const int e = blockIdx.x / cap, r = blockIdx.x - e * cap;
@@ -310,6 +329,11 @@ __global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restric
     }
     TA* dst = rows + (size_t)blockIdx.x * K;
     const TA* src = place >= 0 ? h + (size_t)(pair_at[place] / top) * K : nullptr;
+    if (scale && src) {                                  // rows = scale[pair] * h: the weight on the expert's input
+        const float sc = scale[pair_at[place]];
+        for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = from_f<TA>(sc * to_f<TA>(src[k]));
+        return;
+    }
     const bool wide = ((size_t)K * sizeof(TA)) % 16 == 0 && ((((uintptr_t)h) | ((uintptr_t)rows)) & 15) == 0;
     if (wide) {
         const int n16 = (int)((size_t)K * sizeof(TA) / 16);
@@ -321,13 +345,13 @@ __global__ void moe_gather_kernel(const TA* __restrict__ h, const int* __restric
 }
 
 TL_EXPORT int tl_moe_gather(const void* h, int act_dtype, const int* pair_at, const int* idx, const int* offsets, int cap,
-                            void* rows, int P, int E, int K, int top, cudaStream_t stream) {
+                            void* rows, int P, int E, int K, int top, const float* scale, cudaStream_t stream) {
     (void)idx;
     const long long blocks = cap ? (long long)E * cap : P;
     if (blocks <= 0) return 0;
     if (blocks > 2147483647LL) return 1;
-    if (act_dtype == TL_F32) moe_gather_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>((const float*)h, pair_at, offsets, cap, (float*)rows, K, top);
-    else moe_gather_kernel<bf16><<<(unsigned)blocks, 128, 0, stream>>>((const bf16*)h, pair_at, offsets, cap, (bf16*)rows, K, top);
+    if (act_dtype == TL_F32) moe_gather_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>((const float*)h, pair_at, offsets, cap, (float*)rows, K, top, scale);
+    else moe_gather_kernel<bf16><<<(unsigned)blocks, 128, 0, stream>>>((const bf16*)h, pair_at, offsets, cap, (bf16*)rows, K, top, scale);
     return tl_launch_status();
 }
 
@@ -371,22 +395,27 @@ TL_EXPORT int tl_relu_square(void* u, int act_dtype, long long n, cudaStream_t s
 template <typename TA>
 __global__ void moe_combine_kernel(const TA* __restrict__ rows, const int* __restrict__ place_of, const int* __restrict__ idx,
                                    const int* __restrict__ offsets, int cap, const float* __restrict__ wts,
-                                   TA* __restrict__ y, int N, int top) {
+                                   TA* __restrict__ y, int N, int top, const TA* __restrict__ extra,
+                                   const float* __restrict__ extra_gate, int ldg) {
     const int t = blockIdx.x;
+    const float gt = !extra ? 0.f : extra_gate ? 1.0f / (1.0f + expf(-extra_gate[(size_t)t * ldg])) : 1.0f;
     for (int n = threadIdx.x; n < N; n += blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < top; ++j) {
             const size_t pair = (size_t)t * top + j;
-            acc = fmaf(wts[pair], to_f<TA>(rows[moe_row(place_of[pair], idx[pair], offsets, cap) * N + n]), acc);
+            const float v = to_f<TA>(rows[moe_row(place_of[pair], idx[pair], offsets, cap) * N + n]);
+            acc = wts ? fmaf(wts[pair], v, acc) : acc + v;
         }
+        if (extra) acc = fmaf(gt, to_f<TA>(extra[(size_t)t * N + n]), acc);
         y[(size_t)t * N + n] = from_f<TA>(acc);
     }
 }
 
 TL_EXPORT int tl_moe_combine(const void* rows, int act_dtype, const int* place_of, const int* idx, const int* offsets, int cap,
-                             const float* wts, void* y, int T, int N, int top, cudaStream_t stream) {
+                             const float* wts, void* y, int T, int N, int top, const void* extra, const float* extra_gate, int ldg,
+                             cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (act_dtype == TL_F32) moe_combine_kernel<float><<<T, 256, 0, stream>>>((const float*)rows, place_of, idx, offsets, cap, wts, (float*)y, N, top);
-    else moe_combine_kernel<bf16><<<T, 256, 0, stream>>>((const bf16*)rows, place_of, idx, offsets, cap, wts, (bf16*)y, N, top);
+    if (act_dtype == TL_F32) moe_combine_kernel<float><<<T, 256, 0, stream>>>((const float*)rows, place_of, idx, offsets, cap, wts, (float*)y, N, top, (const float*)extra, extra_gate, ldg);
+    else moe_combine_kernel<bf16><<<T, 256, 0, stream>>>((const bf16*)rows, place_of, idx, offsets, cap, wts, (bf16*)y, N, top, (const bf16*)extra, extra_gate, ldg);
     return tl_launch_status();
 }

@@ -85,8 +85,9 @@ class ModelRunner:
             if isinstance(need, PagedKV):
                 g = cache.group_of[cid]
                 shape = (cache.groups[g].pool.num_pages + 1, need.num_kv_heads, self.page_size, need.head_dim)
-                self.caches[cid] = KVCacheView(torch.zeros(shape, dtype=self.rt.act_dtype, device=self.device),
-                                               torch.zeros(shape, dtype=self.rt.act_dtype, device=self.device), g)
+                k = torch.zeros(shape, dtype=self.rt.act_dtype, device=self.device)
+                v = k if need.shared_values else torch.zeros(shape, dtype=self.rt.act_dtype, device=self.device)
+                self.caches[cid] = KVCacheView(k, v, g)
             elif isinstance(need, SlotState):
                 shape = (cache.max_num_seqs + 1,) + tuple(need.shape)
                 self.caches[cid] = StateView(torch.zeros(shape, dtype=_DTYPES[need.dtype], device=self.device))
@@ -140,7 +141,7 @@ class ModelRunner:
         total = 0
         for c in self.caches.values():
             if isinstance(c, KVCacheView):
-                total += 2 * c.k.shape[1] * c.k.shape[3] * c.k.element_size()
+                total += (1 if c.v is c.k else 2) * c.k.shape[1] * c.k.shape[3] * c.k.element_size()
         return total
 
     # ------------------------------------------------------------------ requests

@@ -14,7 +14,8 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS, POSITION_ENCODINGS, KVCacheView, PartSpec, Runtime
+from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS, POSITION_ENCODINGS, KVCacheView, PartSpec, Runtime, TensorSpec
+from ..parts.linear import with_row
 
 
 @dataclass(frozen=True)
@@ -27,6 +28,7 @@ class LayerSpec:
 class RunEntry:
     layer: int                          # index into ModelSpec.layers
     reads_cache_of: int | None = None   # index of an earlier run entry whose cache this one reads
+    add_row: int | None = None          # row of `ModelSpec.stream_rows` added to the residual stream in front of this entry
 
 
 @dataclass(frozen=True)
@@ -46,6 +48,11 @@ class ModelSpec:
     max_position_embeddings: int | None = None
     embedding: PartSpec = PartSpec("token_table")     # built with vocab= and dim=; another kind may scale its rows
     head: PartSpec = PartSpec("linear")               # built with vocab=, dim= and tied=; another kind may add a bias or a cap
+    embedding_norm: PartSpec | None = None            # a norm of the embedded tokens: the stream starts as its float32 result
+    embedding_norm_prefix: str = "model.embed_norm"
+    stream_rows: int = 0                              # > 0: a table [rows, hidden] of vectors that run entries add to the stream
+    stream_rows_name: str = "model.stream_rows"       # (`RunEntry.add_row`: a pass over shared layers announces its number)
+    stream_rows_eps: float = 1e-6                     # eps of the norms the addend travels to (they fold it into their kernel)
 
 
 class Model:
@@ -59,7 +66,11 @@ class Model:
         self.head = HEADS.build(spec.head, rt, vocab=spec.vocab_size, dim=spec.hidden_size, tied=spec.tie_word_embeddings)
         self.embedding_position = (POSITION_ENCODINGS.build(spec.embedding_position, rt)
                                    if spec.embedding_position else None)
+        self.embedding_norm = NORMS.build(spec.embedding_norm, rt) if spec.embedding_norm else None
+        self.stream_rows = None
         for i, e in enumerate(spec.run):
+            if e.add_row is not None and not 0 <= e.add_row < spec.stream_rows:
+                raise ValueError(f"run entry {i} adds row {e.add_row} of a table of {spec.stream_rows}")
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"run entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
             if e.reads_cache_of is not None and not (0 <= e.reads_cache_of < i
@@ -71,6 +82,10 @@ class Model:
         out = dict(self.embedding.expected_tensors(self.spec.embedding_prefix))
         if self.embedding_position is not None:
             out.update(self.embedding_position.expected_tensors(self.spec.embedding_position_prefix))
+        if self.embedding_norm is not None:
+            out.update(self.embedding_norm.expected_tensors(self.spec.embedding_norm_prefix))
+        if self.spec.stream_rows:
+            out[self.spec.stream_rows_name] = TensorSpec((self.spec.stream_rows, self.spec.hidden_size))
         for block, layer in zip(self.blocks, self.spec.layers):
             out.update(block.expected_tensors(layer.prefix))
         out.update(self.final_norm.expected_tensors(self.spec.final_norm_prefix))
@@ -81,6 +96,10 @@ class Model:
         self.embedding.bind(weights, self.spec.embedding_prefix)
         if self.embedding_position is not None:
             self.embedding_position.bind(weights, self.spec.embedding_position_prefix)
+        if self.embedding_norm is not None:
+            self.embedding_norm.bind(weights, self.spec.embedding_norm_prefix)
+        if self.spec.stream_rows:
+            self.stream_rows = weights[self.spec.stream_rows_name].float().contiguous()      # they join a float32 sum
         for block, layer in zip(self.blocks, self.spec.layers):
             block.bind(weights, layer.prefix)
         self.final_norm.bind(weights, self.spec.final_norm_prefix)
@@ -113,6 +132,8 @@ class Model:
         parts = [self.embedding, self.final_norm, self.head, *self.blocks]
         if self.embedding_position is not None:
             parts.append(self.embedding_position)
+        if self.embedding_norm is not None:
+            parts.append(self.embedding_norm)
         return all(getattr(p, "graph_capturable", False) for p in parts)
 
     # ---- one step
@@ -121,8 +142,12 @@ class Model:
         x = self.embedding.forward(ctx.ids)
         if self.embedding_position is not None:
             self.embedding_position.on_embedding(x, ctx)
+        if self.embedding_norm is not None:
+            x = self.embedding_norm.norm_stream(x)
         pending = None
         for i, e in enumerate(self.spec.run):
+            if e.add_row is not None:
+                pending = with_row(x, pending, self.stream_rows[e.add_row], self.spec.stream_rows_eps)
             if e.reads_cache_of is None:
                 cache = self._cache_of(i, caches)
             else:

@@ -13,14 +13,16 @@ import torch
 
 from .csrc.build import CHECK_BUILD, load_library
 
-CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu", "recurrent.cu", "moe.cu"]
+CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu", "recurrent.cu", "moe.cu",
+                "delta.cu", "latent.cu"]
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 _SIGNATURES = {
     "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
     "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _F, _I, _P],
-    "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
+    "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "tl_post_norm_add_norm": [_P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P],
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong,
                          _I, _P, _P, _F, _I, _I, _P, _P],
     "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _I, _P, _P],
@@ -34,13 +36,20 @@ _SIGNATURES = {
     "tl_head_norm_gate": [_P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
     "tl_sum_normed": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _F, _P],
     "tl_small_proj": [_P, _I, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
-    "tl_topk_softmax": [_P, _I, _I, _P, _P, _I, _P],
-    "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
-    "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "tl_topk_softmax": [_P, _I, _I, _I, _P, _P, _I, _I, _P],
+    "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
     "tl_moe_sort": [_P, _I, _I, _P, _P, _P, _P],
-    "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
+    "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P],
     "tl_relu_square": [_P, _I, ctypes.c_longlong, _P],
-    "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P],
+    "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _P],
+    "tl_conv_prep": [_P, _I, _I, _P, _I, _I, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+    "tl_delta_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "tl_delta_state_floats": [_I],
+    "tl_delta_columns": [],
+    "tl_latent_prep": [_P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "tl_latent_qrot": [_P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "tl_head_matmul": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
 }
 
 
@@ -282,8 +291,11 @@ def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: t
            "add_rmsnorm")
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None) -> None:
-    """out = silu(gate) * up from gu [T, 2I].  block None: gate = gu[:, :I], up = gu[:, I:]; else gate
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu_squared": 2}
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None, act: str = "silu") -> None:
+    """out = act(gate) * up from gu [T, 2I], act "silu" or "gelu_tanh" (the tanh form of gelu).  block None: gate = gu[:, :I], up = gu[:, I:]; else gate
     and up columns alternate in blocks of `block` columns (gate first), as a product against weight rows
     interleaved that way leaves them."""
     T, I = out.shape
@@ -293,7 +305,40 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None) -> N
     if blk <= 0 or I % blk:
         raise KernelError(f"silu_mul: the block of {blk} columns must divide I = {I}")
     _contig(gu, "gu"); _contig(out, "out")
-    _check(core().tl_silu_mul(_ptr(gu), _ptr(out), dtype_code(out.dtype), T, I, blk, _stream()), "silu_mul")
+    if act not in ("silu", "gelu_tanh"):
+        raise KernelError(f"silu_mul: act {act!r} is neither 'silu' nor 'gelu_tanh'")
+    _check(core().tl_silu_mul(_ptr(gu), _ptr(out), dtype_code(out.dtype), T, I, blk, GATE_ACTS[act], _stream()), "silu_mul")
+
+
+def post_norm_add_norm(x: torch.Tensor, a: torch.Tensor | None, w_post: torch.Tensor | None, w_pre: torch.Tensor | None,
+                       out: torch.Tensor | None, eps: float, extra: torch.Tensor | None = None,
+                       rows: torch.Tensor | None = None) -> None:
+    """x += a / rms(a) * w_post (+ extra, float32 [H], once a row); out = x / rms(x) * w_pre; float to the end.
+    x float32 [*, H]; a (or None: no addend) and out (or None: the sum only) of the activation type; the two weights of
+    one type.  `rows` picks the rows that are produced (x is then left alone)."""
+    H = x.shape[-1]
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("post_norm_add_norm: x must be contiguous float32")
+    if (a is None) != (w_post is None) or (out is None) != (w_pre is None):
+        raise KernelError("post_norm_add_norm: an addend comes with its weight, an output with its weight")
+    ws = [w for w in (w_post, w_pre) if w is not None]
+    if any(w.numel() != H or not w.is_contiguous() or w.dtype != ws[0].dtype for w in ws):
+        raise KernelError("post_norm_add_norm: weights must be [H] of one type")
+    if a is not None and (a.shape != x.shape or not a.is_contiguous()):
+        raise KernelError("post_norm_add_norm: a must have x's shape")
+    if a is not None and out is not None and a.dtype != out.dtype:
+        raise KernelError("post_norm_add_norm: a and out must have one type")
+    if extra is not None and (extra.dtype != torch.float32 or extra.numel() != H or not extra.is_contiguous()):
+        raise KernelError("post_norm_add_norm: extra must be float32 [H]")
+    R = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _ints(rows, "rows")
+    if out is not None and (out.shape != (R, H) or not out.is_contiguous()):
+        raise KernelError("post_norm_add_norm: out must be [rows, H]")
+    act = out.dtype if out is not None else a.dtype if a is not None else torch.float32
+    _check(core().tl_post_norm_add_norm(_ptr(x), _ptr(a), _ptr(w_post), _ptr(extra), _ptr(w_pre), dtype_code(ws[0].dtype) if ws else 0,
+                                        _ptr(out), dtype_code(act), _ptr(rows), R, H, float(eps), int(rows is None), _stream()),
+           "post_norm_add_norm")
 
 
 def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tensor, req_slot: torch.Tensor,
@@ -523,37 +568,67 @@ def small_proj(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out:
                                 out.stride(0), T, N, K, _stream()), "small_proj")
 
 
-def topk_softmax(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor) -> None:
-    """Per row of z (float32 [T, E]): the `top` largest entries (lowest index first on a tie) in idx int32 [T, top] and
-    the softmax over those entries alone in wts float32 [T, top]."""
+def topk_softmax(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, scoring: str = "softmax_chosen") -> None:
+    """Per row of z (float32 [T, E], rows may be a column range of a wider tensor): the `top` largest entries (lowest index
+    first on a tie) in idx int32 [T, top]; wts float32 [T, top]: the softmax over those entries alone ("softmax_chosen"),
+    or the sigmoid of each ("sigmoid")."""
     T, E = z.shape
-    if z.dtype != torch.float32 or wts.dtype != torch.float32 or idx.shape != (T, top) or wts.shape != (T, top):
+    if z.dtype != torch.float32 or wts.dtype != torch.float32 or idx.shape != (T, top) or wts.shape != (T, top) or z.stride(1) != 1:
         raise KernelError("topk_softmax: z float32 [T, E], idx int32 [T, top], wts float32 [T, top]")
-    _contig(z, "z"); _ints(idx, "idx"); _contig(wts, "wts")
-    _check(core().tl_topk_softmax(_ptr(z), E, int(top), _ptr(idx), _ptr(wts), T, _stream()), "topk_softmax")
+    if scoring not in ("softmax_chosen", "sigmoid"):
+        raise KernelError(f"topk_softmax: scoring {scoring!r} is neither 'softmax_chosen' nor 'sigmoid'")
+    _ints(idx, "idx"); _contig(wts, "wts")
+    _check(core().tl_topk_softmax(_ptr(z), z.stride(0), E, int(top), _ptr(idx), _ptr(wts), T, int(scoring == "sigmoid"), _stream()),
+           "topk_softmax")
 
 
-def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tensor) -> None:
-    """a[t * top + j, :] = relu(w_up[idx[t, j]] h[t])^2; w_up [E, F, K], a [T * top, F] of h's type."""
+def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tensor, act: str = "relu_squared",
+           gated: bool = False, in_scale: torch.Tensor | None = None) -> None:
+    """a[t * top + j, :] = act(s w_up[idx[t, j]] h[t]); w_up [E, F, K], a [T * top, F] of h's type; s = in_scale[t, j]
+    (float32 [T, top]: the weight on the expert's input) or 1.  `gated`: w_up is [E, 2F, K], an expert's gate rows then its up
+    rows, and a = act(s gate) * (s up)."""
     T, K = h.shape
-    E, F, _ = w_up.shape
     top = idx.shape[1]
-    if w_up.shape[2] != K or a.shape != (T * top, F) or a.dtype != h.dtype:
-        raise KernelError("moe_up: w_up [E, F, K], a [T top, F] of h's type")
+    F = a.shape[1]
+    if w_up.dim() != 3 or w_up.shape[1:] != ((2 * F if gated else F), K) or a.shape != (T * top, F) or a.dtype != h.dtype:
+        raise KernelError("moe_up: w_up [E, F, K] ([E, 2F, K] gated), a [T top, F] of h's type")
+    if act not in GATE_ACTS:
+        raise KernelError(f"moe_up: act {act!r} is not one of {sorted(GATE_ACTS)}")
+    if in_scale is not None and (in_scale.dtype != torch.float32 or in_scale.shape != idx.shape or not in_scale.is_contiguous()):
+        raise KernelError("moe_up: in_scale must be float32 [T, top]")
     _contig(h, "h"); _contig(w_up, "w_up"); _ints(idx, "idx"); _contig(a, "a")
     _check(core().tl_moe_up(_ptr(h), dtype_code(h.dtype), _ptr(w_up), dtype_code(w_up.dtype), _ptr(idx), _ptr(a), T * top, K, F,
-                            top, _stream()), "moe_up")
+                            top, int(gated), GATE_ACTS[act], _ptr(in_scale), _stream()), "moe_up")
 
 
-def moe_down(a: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, y: torch.Tensor) -> None:
-    """y[t] = sum_j wts[t, j] * w_down[idx[t, j]] a[t * top + j]; w_down [E, N, F]."""
+def _extra(extra, gate, y, who):
+    """(pointer of the gate's first element, its row stride) of an addend `sigmoid(gate[t]) * extra[t]`."""
+    if extra is None:
+        if gate is not None:
+            raise KernelError(f"{who}: a gate comes with an addend")
+        return None, 0
+    if extra.shape != y.shape or extra.dtype != y.dtype or not extra.is_contiguous():
+        raise KernelError(f"{who}: the addend must have y's shape and type")
+    if gate is None:
+        return None, 0
+    if gate.dtype != torch.float32 or gate.dim() != 1 or gate.numel() != y.shape[0]:
+        raise KernelError(f"{who}: the gate must be float32, one number a token (a column of a wider tensor may be passed)")
+    return _ptr(gate), gate.stride(0)
+
+
+def moe_down(a: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor | None, y: torch.Tensor,
+             extra: torch.Tensor | None = None, extra_gate: torch.Tensor | None = None) -> None:
+    """y[t] = sum_j wts[t, j] * w_down[idx[t, j]] a[t * top + j] (+ sigmoid(extra_gate[t]) * extra[t]); w_down [E, N, F];
+    wts None: an unweighted sum."""
     T, top = idx.shape
     E, N, F = w_down.shape
-    if a.shape != (T * top, F) or y.shape != (T, N) or y.dtype != a.dtype or wts.dtype != torch.float32 or wts.shape != idx.shape:
+    if a.shape != (T * top, F) or y.shape != (T, N) or y.dtype != a.dtype or \
+            (wts is not None and (wts.dtype != torch.float32 or wts.shape != idx.shape or not wts.is_contiguous())):
         raise KernelError("moe_down: a [T top, F], w_down [E, N, F], y [T, N], wts float32 [T, top]")
-    _contig(a, "a"); _contig(w_down, "w_down"); _ints(idx, "idx"); _contig(wts, "wts"); _contig(y, "y")
+    _contig(a, "a"); _contig(w_down, "w_down"); _ints(idx, "idx"); _contig(y, "y")
+    g_ptr, ldg = _extra(extra, extra_gate, y, "moe_down")
     _check(core().tl_moe_down(_ptr(a), dtype_code(a.dtype), _ptr(w_down), dtype_code(w_down.dtype), _ptr(idx), _ptr(wts), _ptr(y),
-                              T, F, N, top, _stream()), "moe_down")
+                              T, F, N, top, _ptr(extra), g_ptr, ldg, _stream()), "moe_down")
 
 
 def moe_sort(idx: torch.Tensor, E: int):
@@ -568,7 +643,7 @@ def moe_sort(idx: torch.Tensor, E: int):
 
 
 def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, idx: torch.Tensor, offsets: torch.Tensor, top: int, rows: torch.Tensor,
-               cap: int = 0) -> None:
+               cap: int = 0, scale: torch.Tensor | None = None) -> None:
     """rows[row of place] = h[pair_at[place] // top].  cap 0: row = place (rows [P, K], the experts' runs one behind the
     other); cap > 0: every expert has cap rows of its own (rows [E * cap, K], row = expert * cap + place - offsets[expert];
     the rows behind a run are set to zero)."""
@@ -577,8 +652,10 @@ def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, idx: torch.Tensor, offset
     if h.shape[1] != K or rows.dtype != h.dtype or rows.shape[0] != (E * cap if cap else P) or idx.numel() != P:
         raise KernelError("moe_gather: rows [P, K] (or [E cap, K]) of h's type")
     _contig(h, "h"); _contig(rows, "rows"); _ints(pair_at, "pair_at"); _ints(idx, "idx"); _ints(offsets, "offsets")
+    if scale is not None and (scale.dtype != torch.float32 or scale.numel() != P or not scale.is_contiguous()):
+        raise KernelError("moe_gather: scale must be float32, one number a pair (rows = scale * h)")
     _check(core().tl_moe_gather(_ptr(h), dtype_code(h.dtype), _ptr(pair_at), _ptr(idx), _ptr(offsets), int(cap), _ptr(rows), P, E, K,
-                                int(top), _stream()), "moe_gather")
+                                int(top), _ptr(scale), _stream()), "moe_gather")
 
 
 def relu_square(u: torch.Tensor) -> None:
@@ -587,14 +664,134 @@ def relu_square(u: torch.Tensor) -> None:
     _check(core().tl_relu_square(_ptr(u), dtype_code(u.dtype), u.numel(), _stream()), "relu_square")
 
 
-def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, idx: torch.Tensor, offsets: torch.Tensor, wts: torch.Tensor,
-                y: torch.Tensor, cap: int = 0) -> None:
-    """y[t] = sum_j wts[t, j] * rows[row of place_of[t * top + j]]; rows laid out as `moe_gather` lays them out."""
-    T, top = wts.shape
+def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, idx: torch.Tensor, offsets: torch.Tensor, wts: torch.Tensor | None,
+                y: torch.Tensor, cap: int = 0, extra: torch.Tensor | None = None, extra_gate: torch.Tensor | None = None) -> None:
+    """y[t] = sum_j wts[t, j] * rows[row of place_of[t * top + j]] (+ sigmoid(extra_gate[t]) * extra[t]); rows laid out as
+    `moe_gather` lays them out; wts None: an unweighted sum."""
+    T, top = idx.shape
     N = y.shape[1]
     E = offsets.numel() - 1
-    if rows.shape != ((E * cap if cap else T * top), N) or rows.dtype != y.dtype or y.shape[0] != T or wts.dtype != torch.float32:
+    if rows.shape != ((E * cap if cap else T * top), N) or rows.dtype != y.dtype or y.shape[0] != T or \
+            (wts is not None and (wts.dtype != torch.float32 or wts.shape != idx.shape or not wts.is_contiguous())):
         raise KernelError("moe_combine: rows [T top, N] (or [E cap, N]) of y's type, wts float32 [T, top]")
-    _contig(rows, "rows"); _ints(place_of, "place_of"); _ints(idx, "idx"); _ints(offsets, "offsets"); _contig(wts, "wts"); _contig(y, "y")
+    _contig(rows, "rows"); _ints(place_of, "place_of"); _ints(idx, "idx"); _ints(offsets, "offsets"); _contig(y, "y")
+    g_ptr, ldg = _extra(extra, extra_gate, y, "moe_combine")
     _check(core().tl_moe_combine(_ptr(rows), dtype_code(rows.dtype), _ptr(place_of), _ptr(idx), _ptr(offsets), int(cap), _ptr(wts),
-                                 _ptr(y), T, N, top, _stream()), "moe_combine")
+                                 _ptr(y), T, N, top, _ptr(extra), g_ptr, ldg, _stream()), "moe_combine")
+
+
+# ---------------------------------------------------------------------------------------------
+# The gated delta rule (csrc/delta.cu)
+
+def delta_state_floats(d: int) -> int:
+    """Floats of state that `delta_scan` keeps per (head, slice of `delta_columns()` value columns) for heads of d rows."""
+    n = core().tl_delta_state_floats(int(d))
+    if n <= 0:
+        raise KernelError(f"delta_scan: heads of {d} rows are not supported (at most 256)")
+    return n
+
+
+def delta_columns() -> int:
+    return core().tl_delta_columns()
+
+
+def conv_prep(proj: torch.Tensor, taps_w: torch.Tensor, conv_state: torch.Tensor | None, q_start: torch.Tensor,
+              slots: torch.Tensor, out: torch.Tensor, *, B: int, max_q_len: int, nqk: int, d: int, nv: int, dv: int,
+              unit_eps: float, q_scale: float) -> None:
+    """The first C = 2 nqk d + nv dv columns of `proj` (q heads, k heads, v heads) through a causal convolution over time
+    per channel (taps_w [C, taps], the last tap on the current token; the taps - 1 inputs before the step come from
+    `conv_state[slot]`, float32 [taps - 1, C], which is then brought up to date) and silu; every q and k head scaled to
+    unit length, x / sqrt(sum x^2 + unit_eps), q also by q_scale.  out float32 [T, C]."""
+    T = proj.shape[0]
+    C = 2 * nqk * d + nv * dv
+    taps = taps_w.shape[1]
+    if taps_w.shape != (C, taps) or proj.shape[1] < C or proj.stride(1) != 1 or out.shape != (T, C) or out.dtype != torch.float32:
+        raise KernelError("conv_prep: proj [T, >= C], taps_w [C, taps], out float32 [T, C]")
+    _contig(taps_w, "taps_w"); _contig(out, "out"); _ints(q_start, "q_start"); _ints(slots, "slots")
+    slot_stride = 0
+    if taps > 1:
+        if conv_state is None or conv_state.dtype != torch.float32 or not conv_state.is_contiguous() or \
+                conv_state[0].numel() != (taps - 1) * C:
+            raise KernelError("conv_prep: conv_state must be float32 [slots, (taps - 1) * C]")
+        slot_stride = conv_state[0].numel()
+    _check(core().tl_conv_prep(_ptr(proj), dtype_code(proj.dtype), proj.stride(0), _ptr(taps_w), dtype_code(taps_w.dtype), taps,
+                               _ptr(conv_state) if taps > 1 else None, slot_stride, _ptr(q_start), _ptr(slots), _ptr(out), int(B),
+                               int(max_q_len), nqk, d, nv, dv, float(unit_eps), float(q_scale), _stream()), "conv_prep",
+           launches=2 if taps > 1 else 1)
+
+
+def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
+               q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, *, B: int, H: int, nqk: int, d: int, dv: int) -> None:
+    """Per (request, head), tokens in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
+    beta = sigmoid(gates[t, h]) and g = exp(-exp(A_log[h]) softplus(gates[t, H + h] + dt_bias[h])).  qkv float32 [T, C] as
+    `conv_prep` leaves it (q [nqk, d], k [nqk, d], v [H, dv]; head h reads q/k head h // (H / nqk)); the state is read from
+    and left in `state[slot]` (float32, `delta_state_floats` per head and column slice); out float32 [T, H dv]."""
+    T = qkv.shape[0]
+    C = 2 * nqk * d + H * dv
+    if qkv.dtype != torch.float32 or qkv.shape != (T, C) or out.dtype != torch.float32 or out.shape != (T, H * dv):
+        raise KernelError("delta_scan: qkv float32 [T, 2 nqk d + H dv], out float32 [T, H dv]")
+    if gates.dtype != torch.float32 or gates.shape[0] != T or gates.shape[1] < 2 * H or gates.stride(1) != 1:
+        raise KernelError("delta_scan: gates must be float32 [T, >= 2H]")
+    for name, t in (("A_log", A_log), ("dt_bias", dt_bias)):
+        if t.dtype != torch.float32 or t.numel() != H or not t.is_contiguous():
+            raise KernelError(f"delta_scan: {name} must be float32 [H]")
+    _contig(qkv, "qkv"); _contig(out, "out"); _contig(state, "state"); _ints(q_start, "q_start"); _ints(slots, "slots")
+    per_slot = H * -(-dv // delta_columns()) * delta_state_floats(d)
+    if state.dtype != torch.float32 or state[0].numel() != per_slot:
+        raise KernelError(f"delta_scan: a slot holds {state[0].numel()} floats, these sizes need {per_slot}")
+    _check(core().tl_delta_scan(_ptr(qkv), C, 0, nqk * d, 2 * nqk * d, _ptr(gates), gates.stride(0), _ptr(A_log), _ptr(dt_bias),
+                                _ptr(state), per_slot, _ptr(q_start), _ptr(slots), _ptr(out), int(B), H, nqk, d, dv, _stream()),
+           "delta_scan")
+
+
+# ---------------------------------------------------------------------------------------------
+# Attention through a latent (csrc/latent.cu)
+
+def latent_prep(down: torch.Tensor, qr: int, rank: int, dr: int, wq: torch.Tensor, wkv: torch.Tensor, eps: float,
+                inv_freq: torch.Tensor, rot: int, pos: torch.Tensor, req_slot: torch.Tensor, table: torch.Tensor, page_size: int,
+                cq: torch.Tensor, k_pages: torch.Tensor, write_kv: bool = True) -> None:
+    """Per token, from down float32 [T, qr + rank + dr]: cq = the first qr columns RMS-normalised times wq; into the token's
+    place in k_pages [pages, 1, page, d]: the next `rank` columns RMS-normalised times wkv, then the last dr columns with their
+    first `rot` rotated by position (pairs (i, i + rot/2)), then zeros up to d."""
+    T = down.shape[0]
+    d = k_pages.shape[-1]
+    if down.dtype != torch.float32 or down.shape != (T, qr + rank + dr) or cq.shape != (T, qr) or cq.dtype != k_pages.dtype:
+        raise KernelError("latent_prep: down float32 [T, qr + rank + dr], cq [T, qr] of the pages' type")
+    if tuple(k_pages.shape[1:3]) != (1, page_size) or rank + dr > d:
+        raise KernelError("latent_prep: k_pages must be [pages, 1, page, d >= rank + dr]")
+    if wq.numel() != qr or wkv.numel() != rank or wq.dtype != wkv.dtype:
+        raise KernelError("latent_prep: the norms' weights must be [qr] and [rank] of one type")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2:
+        raise KernelError("latent_prep: inv_freq must be float32 [rot/2]")
+    _contig(down, "down"); _contig(cq, "cq"); _contig(k_pages, "k_pages"); _contig(wq, "wq"); _contig(wkv, "wkv")
+    _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
+    _check(core().tl_latent_prep(_ptr(down), qr, rank, dr, _ptr(wq), _ptr(wkv), dtype_code(wq.dtype), float(eps), _ptr(inv_freq),
+                                 int(rot), _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size, _ptr(cq),
+                                 _ptr(k_pages), dtype_code(cq.dtype), d, int(write_kv), T, table.shape[0], k_pages.shape[0],
+                                 fault_words(down.device), _stream()), "latent_prep")
+
+
+def latent_qrot(q: torch.Tensor, dk: int, dr: int, inv_freq: torch.Tensor, rot: int, pos: torch.Tensor, qa: torch.Tensor,
+                rank: int, H: int) -> None:
+    """qa[t, h, rank : rank + dr] = q[t, h, dk : dk + dr] with its first `rot` dimensions rotated by position; the columns of
+    qa behind them are set to zero.  q [T, H (dk + dr)], qa [T, H d]."""
+    T = q.shape[0]
+    d = qa.shape[1] // H
+    if q.shape != (T, H * (dk + dr)) or qa.shape != (T, H * d) or qa.dtype != q.dtype or rank + dr > d:
+        raise KernelError("latent_qrot: q [T, H (dk + dr)], qa [T, H d] of one type, d >= rank + dr")
+    _contig(q, "q"); _contig(qa, "qa"); _ints(pos, "pos")
+    _check(core().tl_latent_qrot(_ptr(q), dk, dr, _ptr(inv_freq), int(rot), _ptr(pos), _ptr(qa), rank, d, H, T, dtype_code(q.dtype),
+                                 _stream()), "latent_qrot")
+
+
+def head_matmul(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, H: int, K: int, N: int, x_head_stride: int,
+                y_head_stride: int) -> None:
+    """y[t, h, :N] = x[t, h, :K] w[h]; w [H, K, N]; head h of row t starts at x[t, h * x_head_stride] (y alike); float sums."""
+    T = x.shape[0]
+    if w.shape != (H, K, N) or x.dtype != y.dtype or y.shape[0] != T or x.stride(1) != 1 or y.stride(1) != 1:
+        raise KernelError("head_matmul: w [H, K, N], x and y of one type with unit inner stride")
+    if (H - 1) * x_head_stride + K > x.shape[1] or (H - 1) * y_head_stride + N > y.shape[1]:
+        raise KernelError("head_matmul: the heads do not lie inside the rows")
+    _contig(w, "w")
+    _check(core().tl_head_matmul(_ptr(x), x.stride(0), x_head_stride, _ptr(w), dtype_code(w.dtype), _ptr(y), y.stride(0),
+                                 y_head_stride, T, H, K, N, dtype_code(x.dtype), _stream()), "head_matmul")

@@ -9,7 +9,7 @@ first norm (or the model's last) as `pending`.
 from __future__ import annotations
 
 from .base import FEED_FORWARDS, MIXERS, NORMS, Part, PartSpec, Runtime, register_block
-from .linear import Scaled
+from .linear import PostNormed, Scaled, resolve
 
 
 @register_block("pre_norm")
@@ -77,3 +77,51 @@ class PreNormBlock(Part):
         if getattr(consumer, "accepts_normed_input", False) and getattr(norm, "can_defer", False):
             return norm.add_norm(x, pending, defer=True)
         return norm.add_norm(x, pending)
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(PreNormBlock):
+    """A pre-norm block whose sub-blocks are normalised once more on their way into the residual stream:
+
+        x += norm1b(mixer(norm1(x)));   x += norm2b(feed_forward(norm2(x)))
+
+    A sub-block's output travels as a `PostNormed` addend: its own norm, the residual sum and the next norm are one kernel
+    in float32.  The second norms are the layer's `norm1b` / `norm2b` tensors (plain weights, the first norms' eps)."""
+
+    def __init__(self, rt: Runtime, mixer: PartSpec, feed_forward: PartSpec | None, norm1: PartSpec, norm2: PartSpec | None,
+                 post_norm1: PartSpec, post_norm2: PartSpec | None, names: dict | None = None):
+        super().__init__(rt, mixer, feed_forward, norm1, norm2,
+                         {"post_norm1": "norm1b", "post_norm2": "norm2b", **(names or {})})
+        self.post1 = NORMS.build(post_norm1, rt)
+        self.post2 = NORMS.build(post_norm2, rt) if post_norm2 is not None else None
+
+    def _children(self, prefix):
+        n = self.names
+        parts = ((self.post1, f"{prefix}.{n['post_norm1']}"), (self.post2, f"{prefix}.{n['post_norm2']}"))
+        return super()._children(prefix) + tuple((part, p) for part, p in parts if part is not None)
+
+    def expected_tensors(self, prefix):
+        import dataclasses
+        out = super().expected_tensors(prefix)
+        if self.ff is None and self.post2 is not None:
+            for k, v in self.post2.expected_tensors(f"{prefix}.{self.names['post_norm2']}").items():
+                out[k] = dataclasses.replace(v, optional=True)
+        return out
+
+    def bind(self, weights, prefix):
+        for part, p in self._children(prefix):
+            if self.ff is None and (part is self.norm2 or part is self.post2):
+                continue
+            part.bind(weights, p)
+
+    @property
+    def graph_capturable(self) -> bool:
+        return super().graph_capturable
+
+    def forward(self, x, pending, ctx, cache):
+        h = self.norm1.add_norm(x, pending)
+        a = PostNormed(self.mixer.forward(h, ctx, cache), self.post1.weight, self.post1.eps)
+        if self.ff is None:
+            return a
+        h = self.norm2.add_norm(x, a)
+        return PostNormed(self.ff.forward(h, ctx), self.post2.weight, self.post2.eps)

@@ -1,0 +1,96 @@
+"""Attention through a latent: the cache holds, per token, one normalised latent vector c and one rotated key part r.
+
+    cq = norm(Wdq h; w_dq),  q = Wuq cq              per head [dk plain | dr to rotate]
+    Wdkv h = [rank | dr]:    c = norm(first; w_dkv),  r = rot(rest, position)      one r for all heads
+    k_head = Wuk_head c,  v_head = Wuv_head c
+    score(t, j) = scale (q_plain . k_head(j) + rot(q_rot) . r(j)),  softmax over the window,  y = Wo [sum_j p_j v_head(j)]
+
+Only c and r are cached.  The scores and the weighted sums are taken in the latent's space, which is the same arithmetic in
+another order:  q_plain . (Wuk c) = (Wuk^T q_plain) . c  and  sum_j p_j Wuv c_j = Wuv (sum_j p_j c_j).  The pages then look
+like ONE key/value head of size rank + dr (padded to what the attention kernels take) whose value is the key row itself, so
+every paged attention kernel of the package serves this mixer unchanged (the value pages are the key pages: a token is
+stored once); the output's first `rank` columns are sum_j p_j c_j, the rest is not read.  The two changes of space are
+products per head (`ops.head_matmul`).  Norm statistics, angles, scores and softmax are float32 in both engines.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache import PagedKV
+from .base import POSITION_ENCODINGS, KVCacheView, Part, PartSpec, Rotary, Runtime, TensorSpec, register_mixer
+from .linear import matmul, resolve
+
+_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o"}
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Part):
+    graph_capturable = True
+
+    def __init__(self, rt: Runtime, hidden: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int, q_rank: int,
+                 kv_rank: int, scale: float, norm_eps: float, position: PartSpec, window: int | None = None,
+                 names: dict | None = None):
+        super().__init__(rt)
+        self.hidden, self.H, self.dk, self.dr, self.dv = hidden, num_heads, head_dim, rot_dim, v_head_dim
+        self.qr, self.rank, self.scale, self.eps, self.window = q_rank, kv_rank, float(scale), float(norm_eps), window
+        d = kv_rank + rot_dim
+        self.d = d if rt.exact else -(-d // 16) * 16     # the bfloat16 attention kernels take multiples of 16
+        self.position = POSITION_ENCODINGS.build(position, rt, head_dim=rot_dim)
+        self.names = {**_NAMES, **(names or {})}
+        # what `attention_kernels.attend` reads of a mixer
+        self.nq, self.nkv, self.sink = num_heads, 1, None
+        self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.n_q = self.n_kv = None
+
+    def cache_need(self):
+        return PagedKV(1, self.d, self.window, shared_values=True)
+
+    def expected_tensors(self, prefix):
+        n = {k: f"{prefix}.{v}" for k, v in self.names.items()}
+        W, H = self.hidden, self.H
+        return {n["dq"]: TensorSpec((self.qr, W)), n["dq_norm"]: TensorSpec((self.qr,), init="ones"),
+                n["uq"]: TensorSpec((H * (self.dk + self.dr), self.qr)),
+                n["dkv"]: TensorSpec((self.rank + self.dr, W)), n["dkv_norm"]: TensorSpec((self.rank,), init="ones"),
+                n["uk"]: TensorSpec((H * self.dk, self.rank)), n["uv"]: TensorSpec((H * self.dv, self.rank)),
+                n["o"]: TensorSpec((W, H * self.dv))}
+
+    def bind(self, weights, prefix):
+        n = {k: f"{prefix}.{v}" for k, v in self.names.items()}
+        H = self.H
+        # the down product's float32 accumulators are kept as they are: they feed two norms
+        self.w_down = self._compute_copy(torch.cat([weights[n["dq"]], weights[n["dkv"]]], dim=0))
+        self.w_uq = self._compute_copy(weights[n["uq"]])
+        self.w_uk = self._compute_copy(weights[n["uk"]].view(H, self.dk, self.rank))                       # [H, K = dk, N = rank]
+        self.w_uv = self._compute_copy(weights[n["uv"]].view(H, self.dv, self.rank).transpose(1, 2))       # [H, K = rank, N = dv]
+        self.w_o = self._compute_copy(weights[n["o"]])
+        self.n_q = weights[n["dq_norm"]].contiguous()
+        self.n_kv = weights[n["dkv_norm"]].to(self.n_q.dtype).contiguous()
+
+    def forward(self, h, ctx, cache):
+        H, d, dk, dr, rank = self.H, self.d, self.dk, self.dr, self.rank
+        T = h.shape[0]
+        act = self.rt.act_dtype
+        rotary = self.position.rotary()
+        if not isinstance(rotary, Rotary):
+            rotary = Rotary(*rotary)
+        if rotary.pairing != "half":
+            raise NotImplementedError("latent_attention rotates pairs (i, i + rot/2)")
+        table = ctx.tables[cache.group]
+        down = self._down(h)
+        cq = torch.empty((T, self.qr), dtype=act, device=down.device)
+        ops.latent_prep(down, self.qr, rank, dr, self.n_q, self.n_kv, self.eps, rotary.inv_freq, rotary.rot, ctx.pos, ctx.req_slot,
+                        table, ctx.page_size, cq, cache.k, write_kv=cache.owner)
+        q = resolve(matmul(cq, self.w_uq))
+        qa = torch.empty((T, H * d), dtype=act, device=q.device)
+        ops.head_matmul(q, self.w_uk, qa, H, dk, rank, dk + dr, d)
+        ops.latent_qrot(q, dk, dr, rotary.inv_freq, rotary.rot, ctx.pos, qa, rank, H)
+        o = torch.empty((T, H * d), dtype=act, device=q.device)
+        from . import attention_kernels
+        attention_kernels.attend(self, qa, o, ctx, KVCacheView(cache.k, cache.k, cache.group, cache.owner), table)
+        ov = torch.empty((T, H * self.dv), dtype=act, device=q.device)
+        ops.head_matmul(o, self.w_uv, ov, H, rank, self.dv, d, self.dv)
+        return matmul(ov, self.w_o)
+
+    def _down(self, h):
+        """[Wdq; Wdkv] h as float32 [T, qr + rank + dr]."""
+        return resolve(matmul(resolve(h), self.w_down, out_dtype=torch.float32))

@@ -116,8 +116,47 @@ class Scaled:
         self.dtype, self.shape = self.value.dtype, self.value.shape
 
 
+class PostNormed:
+    """An addend of the residual stream that is normalised on its way in: x += value / rms(value) * weight (+ `extra`, a
+    float32 row added once to every row of x).  The norm that does the sum takes both steps and its own into one kernel
+    (`ops.post_norm_add_norm`), everything in float32; anyone else calls `resolve`.  `value` None: only `extra` is added."""
+
+    def __init__(self, value, weight, eps: float, extra=None):
+        self.value = None if value is None else resolve(value)
+        self.weight, self.eps, self.extra = weight, float(eps), extra
+        if self.value is not None:
+            self.dtype, self.shape = self.value.dtype, self.value.shape
+
+    def add_into(self, x: torch.Tensor) -> None:
+        """x += the addend, nothing else."""
+        if self.value is not None or self.extra is not None:
+            ops.post_norm_add_norm(x, self.value, self.weight if self.value is not None else None, None, None, self.eps,
+                                   extra=self.extra)
+
+    def materialize(self) -> torch.Tensor:
+        x = torch.zeros(self.shape, dtype=torch.float32, device=self.value.device)
+        self.add_into(x)
+        return x.to(self.dtype)
+
+
+def with_row(x: torch.Tensor, pending, row: torch.Tensor, eps: float):
+    """`pending` with one more addend: the float32 vector `row`, added once to every row of the stream x."""
+    if pending is None:
+        return PostNormed(None, None, eps, extra=row)
+    if isinstance(pending, PostNormed) and pending.extra is None:
+        pending.extra = row
+        return pending
+    if isinstance(pending, PostNormed):
+        pending.add_into(x)
+    else:
+        x.add_(resolve(pending).float())
+    return PostNormed(None, None, eps, extra=row)
+
+
 def resolve(t):
     """A tensor from what a projection or a norm returned."""
+    if isinstance(t, PostNormed):
+        return t.materialize()
     if isinstance(t, Scaled):
         return (t.value.float() * t.alpha).to(t.dtype)
     if isinstance(t, PendingProduct):

@@ -1,4 +1,4 @@
-"""Dense gated feed-forward: y = (act(h Wg^T) * (h Wu^T)) Wd^T, act = silu, no biases.
+"""Dense gated feed-forward: y = (act(h Wg^T) * (h Wu^T)) Wd^T, act = silu or the tanh form of gelu, no biases.
 
 tzar-beep/Tensorline calls the installed package's module for this (tensorline/paged.py:276;
 shapes tensorline/manager.py:53-54).  Here gate and up are one product against the stacked
@@ -21,20 +21,22 @@ class GatedMLP(Part):
     graph_capturable = True
     accepts_normed_input = True         # `h` may be a `NormedInput`: the gate|up product normalises it on the fly
 
-    def __init__(self, rt: Runtime, hidden: int, intermediate: int, activation: str = "silu"):
+    def __init__(self, rt: Runtime, hidden: int, intermediate: int, activation: str = "silu", names: dict | None = None):
+        """`names`: the three tensors' names under the part's prefix (keys gate, up, down)."""
         super().__init__(rt)
-        if activation != "silu":
-            raise ValueError(f"gated_mlp runs 'silu', not {activation!r}")
-        self.hidden, self.intermediate = hidden, intermediate
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated_mlp runs 'silu' or 'gelu_tanh', not {activation!r}")
+        self.hidden, self.intermediate, self.activation = hidden, intermediate, activation
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
         self.w_gate_up = self.w_down = None
 
     def expected_tensors(self, prefix):
-        H, I = self.hidden, self.intermediate
-        return {f"{prefix}.gate_proj.weight": TensorSpec((I, H)), f"{prefix}.up_proj.weight": TensorSpec((I, H)),
-                f"{prefix}.down_proj.weight": TensorSpec((H, I))}
+        H, I, n = self.hidden, self.intermediate, self.names
+        return {f"{prefix}.{n['gate']}": TensorSpec((I, H)), f"{prefix}.{n['up']}": TensorSpec((I, H)),
+                f"{prefix}.{n['down']}": TensorSpec((H, I))}
 
     def bind(self, weights, prefix):
-        g, u = weights[f"{prefix}.gate_proj.weight"], weights[f"{prefix}.up_proj.weight"]
+        g, u = weights[f"{prefix}.{self.names['gate']}"], weights[f"{prefix}.{self.names['up']}"]
         I, H = self.intermediate, self.hidden
         # bfloat16 engine, I % 64 == 0: gate and up rows alternate in blocks of 64, so that a 128-row tile of
         # the tcgen05 product holds both halves of 64 output columns and its epilogue can apply the activation
@@ -44,24 +46,25 @@ class GatedMLP(Part):
             self.w_gate_up = self._compute_copy(gu.reshape(2 * I, H))
         else:
             self.w_gate_up = self._compute_copy(torch.cat((g, u), dim=0))
-        self.w_down = self._compute_copy(weights[f"{prefix}.down_proj.weight"])
+        self.w_down = self._compute_copy(weights[f"{prefix}.{self.names['down']}"])
 
     def forward(self, h, ctx):
         I = self.intermediate
         if isinstance(h, NormedInput) and h.rows is not None:
             h = h.materialize()
-        if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_tc(h.shape[0], 2 * I, self.hidden):
+        silu = self.activation == "silu"                 # the products' own epilogues apply silu only
+        if silu and self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_tc(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
             if ops_gemm.can_gate(h.shape[0], 2 * I, self.hidden):          # the activation inside the product
                 m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=True)
                 return matmul(m, self.w_down, may_defer=True, to_residual=True)
         if isinstance(h, NormedInput):                   # only the few-token products above take the recipe
             h = h.materialize()
-        if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_pair_product(h.shape[0], 2 * I, self.hidden):
+        if silu and self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_pair_product(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
             m = ops_gemm.gemm_tc2(h, self.w_gate_up, gated=True)          # long steps: pairs of blocks, activation in the epilogue
             return matmul(m, self.w_down, may_defer=True)
         gu = matmul(h, self.w_gate_up)
         m = torch.empty((h.shape[0], I), dtype=h.dtype, device=h.device)
-        ops.silu_mul(gu, m, block=self.block)
+        ops.silu_mul(gu, m, block=self.block, act=self.activation)
         return matmul(m, self.w_down, may_defer=True, to_residual=True)          # the next norm adds it up

@@ -4,6 +4,13 @@
     chosen: the `top` largest z;         weights = softmax over the chosen logits only
     y = sum_j weight_j * Wdown[e_j] act(Wup[e_j] h)          experts without biases, act = relu(.)^2
 
+Options, all parameters of the one part: gated experts (`gated`: Wdown (act(Wgate x) * Wup x), tensors `gate`, `up`, `down`),
+the activation (`relu_squared`, `silu`, `gelu_tanh`), the weights as the sigmoid of each chosen logit instead of the softmax
+over the chosen (`scoring` "sigmoid": not renormalised), the weight on the expert's input instead of its output
+(`weight_on` "input": y = sum_j expert_j(weight_j h), which differs because an expert is not linear), no router bias, and a
+shared expert (`shared_inner`: one more gated unit of that size that every token runs, multiplied by sigmoid(w_sg . h), one
+number a token; its row `sg` rides in the router's product).
+
 The experts' matrices are stacked ([E, F, K] and [E, K, F]) at load time.  Steps of few tokens stream, for every
 (token, chosen expert) pair, that expert's rows (`ops.moe_up`, `ops.moe_down`): nothing is sorted and nothing comes
 back to the host, so the step sits in a CUDA graph.  Steps of many tokens sort the pairs by expert on the device,
@@ -31,14 +38,24 @@ class RoutedExperts(Part):
     graph_capturable = True              # a captured step streams the experts whatever its size (see forward)
 
     def __init__(self, rt: Runtime, hidden: int, inner: int, experts: int, top: int, activation: str = "relu_squared",
-                 router_bias: bool = True, names: dict | None = None):
+                 router_bias: bool = True, names: dict | None = None, gated: bool = False, scoring: str = "softmax_chosen",
+                 weight_on: str = "output", shared_inner: int | None = None):
         super().__init__(rt)
-        if activation != "relu_squared":
-            raise ValueError(f"routed_experts runs 'relu_squared', not {activation!r}")
+        if activation not in ops.GATE_ACTS:
+            raise ValueError(f"routed_experts runs one of {sorted(ops.GATE_ACTS)}, not {activation!r}")
+        if scoring not in ("softmax_chosen", "sigmoid") or weight_on not in ("output", "input"):
+            raise ValueError(f"routed_experts: scoring {scoring!r} / weight_on {weight_on!r} are not known")
         if not 1 <= top <= min(experts, 32) or experts > 1024:
             raise ValueError(f"routed_experts: top {top} of {experts} experts is outside what the choice kernel takes")
         self.hidden, self.inner, self.E, self.top, self.router_bias = hidden, inner, experts, top, router_bias
-        self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}", "up": "up", "down": "down", **(names or {})}
+        self.activation, self.gated, self.scoring, self.weight_on = activation, bool(gated), scoring, weight_on
+        self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}", "up": "up", "down": "down", "gate": "gate",
+                      "shared": "shared", "shared_gate": "shared.sg", **(names or {})}
+        self.shared = None
+        if shared_inner is not None:
+            from .mlp import GatedMLP
+            self.shared = GatedMLP(rt, hidden, shared_inner, activation,
+                                   {k: self.names[k] for k in ("gate", "up", "down")})
         self.w_router = self.b_router = self.w_up = self.w_down = None
 
     def _expert(self, prefix, e, which):
@@ -49,41 +66,71 @@ class RoutedExperts(Part):
         if self.router_bias:
             out[f"{prefix}.{self.names['router_bias']}"] = TensorSpec((self.E,))
         for e in range(self.E):
+            if self.gated:
+                out[self._expert(prefix, e, "gate")] = TensorSpec((self.inner, self.hidden))
             out[self._expert(prefix, e, "up")] = TensorSpec((self.inner, self.hidden))
             out[self._expert(prefix, e, "down")] = TensorSpec((self.hidden, self.inner))
+        if self.shared is not None:
+            out.update(self.shared.expected_tensors(f"{prefix}.{self.names['shared']}"))
+            out[f"{prefix}.{self.names['shared_gate']}"] = TensorSpec((1, self.hidden))
         return out
 
     def bind(self, weights, prefix):
-        self.w_router = weights[f"{prefix}.{self.names['router']}"].contiguous()
+        w_router = weights[f"{prefix}.{self.names['router']}"]
         if self.router_bias:
-            self.b_router = weights[f"{prefix}.{self.names['router_bias']}"].to(self.w_router.dtype).contiguous()
-        self.w_up = self._compute_copy(torch.stack([weights[self._expert(prefix, e, "up")] for e in range(self.E)]))
+            self.b_router = weights[f"{prefix}.{self.names['router_bias']}"].to(w_router.dtype)
+        if self.shared is not None:                      # the shared expert's gate is one more row of the router's product
+            self.shared.bind(weights, f"{prefix}.{self.names['shared']}")
+            w_router = torch.cat([w_router, weights[f"{prefix}.{self.names['shared_gate']}"].to(w_router.dtype).view(1, -1)])
+            if self.b_router is not None:
+                self.b_router = torch.cat([self.b_router, self.b_router.new_zeros(1)])
+        self.w_router = w_router.contiguous()
+        if self.b_router is not None:
+            self.b_router = self.b_router.contiguous()
+
+        def stacked(e):                                  # a gated expert: its gate rows, then its up rows
+            up = weights[self._expert(prefix, e, "up")]
+            return torch.cat([weights[self._expert(prefix, e, "gate")], up]) if self.gated else up
+
+        self.w_up = self._compute_copy(torch.stack([stacked(e) for e in range(self.E)]))
         self.w_down = self._compute_copy(torch.stack([weights[self._expert(prefix, e, "down")] for e in range(self.E)]))
 
     def forward(self, h, ctx):
         h = resolve(h)
-        T, top = h.shape[0], self.top
-        z = torch.empty((T, self.E), dtype=torch.float32, device=h.device)
+        T, top, E = h.shape[0], self.top, self.E
+        z = torch.empty((T, self.w_router.shape[0]), dtype=torch.float32, device=h.device)
         ops.small_proj(h, self.w_router, self.b_router, z)
         idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
         wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
-        ops.topk_softmax(z, top, idx, wts)
+        ops.topk_softmax(z[:, :E], top, idx, wts, scoring=self.scoring)
+        extra = extra_gate = None
+        if self.shared is not None:
+            extra, extra_gate = resolve(self.shared.forward(h, ctx)), z[:, E]
+        on_input = self.weight_on == "input"
         y = torch.empty((T, self.hidden), dtype=h.dtype, device=h.device)
         if T <= STREAM_MAX_TOKENS or ctx.graph_max_ctx or self.rt.exact:
             a = torch.empty((T * top, self.inner), dtype=h.dtype, device=h.device)
-            ops.moe_up(h, self.w_up, idx, a)
-            ops.moe_down(a, self.w_down, idx, wts, y)
+            ops.moe_up(h, self.w_up, idx, a, act=self.activation, gated=self.gated, in_scale=wts if on_input else None)
+            ops.moe_down(a, self.w_down, idx, None if on_input else wts, y, extra=extra, extra_gate=extra_gate)
             return y
-        offsets, place_of, pair_at = ops.moe_sort(idx, self.E)
+        offsets, place_of, pair_at = ops.moe_sort(idx, E)
         bounds = offsets.tolist()                        # the one read-back of the step: where every expert's run ends
-        longest = max(bounds[e + 1] - bounds[e] for e in range(self.E))
+        longest = max(bounds[e + 1] - bounds[e] for e in range(E))
         cap = -(-longest // 64) * 64                     # rows every expert gets in the batched products
-        rows = torch.empty((self.E * cap, self.hidden), dtype=h.dtype, device=h.device)
-        ops.moe_gather(h, pair_at, idx, offsets, top, rows, cap=cap)
-        inner = torch.bmm(rows.view(self.E, cap, self.hidden), self.w_up.transpose(1, 2))      # [E, cap, F]
+        rows = torch.empty((E * cap, self.hidden), dtype=h.dtype, device=h.device)
+        ops.moe_gather(h, pair_at, idx, offsets, top, rows, cap=cap, scale=wts.view(-1) if on_input else None)
+        inner = torch.bmm(rows.view(E, cap, self.hidden), self.w_up.transpose(1, 2))             # [E, cap, F] or [E, cap, 2F]
         ops.mark("library product")
-        ops.relu_square(inner)
+        if self.gated:
+            act = torch.empty((E * cap, self.inner), dtype=h.dtype, device=h.device)
+            ops.silu_mul(inner.view(E * cap, 2 * self.inner), act, act=self.activation)
+            inner = act.view(E, cap, self.inner)
+        elif self.activation == "relu_squared":
+            ops.relu_square(inner)
+        else:
+            raise NotImplementedError(f"long steps of experts without a gate run 'relu_squared', not {self.activation!r}")
         outs = torch.bmm(inner, self.w_down.transpose(1, 2))                                    # [E, cap, K]
         ops.mark("library product")
-        ops.moe_combine(outs.view(self.E * cap, self.hidden), place_of, idx, offsets, wts, y, cap=cap)
+        ops.moe_combine(outs.view(E * cap, self.hidden), place_of, idx, offsets, None if on_input else wts, y, cap=cap,
+                        extra=extra, extra_gate=extra_gate)
         return y

@@ -5,7 +5,7 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_norm, tensor_name
-from .linear import FUSE_NORMS, NormedInput, PendingProduct, Scaled, SplitSum, resolve
+from .linear import FUSE_NORMS, NormedInput, PendingProduct, PostNormed, Scaled, SplitSum, resolve
 
 
 @register_norm("rms_norm")
@@ -31,9 +31,27 @@ class RMSNorm(Part):
         w = weights[tensor_name(prefix, self.tensor)]
         self.weight = (1.0 + w.float()).contiguous() if self.one_plus else w.contiguous()      # else in its stored type
 
+    def norm_stream(self, x):
+        """The float32 stream itself normalised, x <- norm(x), nothing rounded (a norm right behind the embedding)."""
+        out = torch.empty_like(x)
+        ops.add_rmsnorm(x, None, self.weight, out, self.eps, cast_first=False)
+        return out
+
     def add_norm(self, x, pending, rows=None, defer=False):
         """`defer`: the caller's next step is a product that takes a `NormedInput`."""
         n = x.shape[0] if rows is None else rows.numel()
+        if isinstance(pending, PostNormed):              # x += value / rms(value) * its weight (+ a row), then this norm
+            if self.cast_first or self.one_plus or pending.eps != self.eps or \
+                    (pending.weight is not None and pending.weight.dtype != self.weight.dtype):
+                if rows is not None:
+                    raise NotImplementedError("a normalised addend before a norm of picked rows needs this norm's float form")
+                pending.add_into(x)
+                pending = None
+            else:
+                h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
+                ops.post_norm_add_norm(x, pending.value, pending.weight if pending.value is not None else None, self.weight, h,
+                                       self.eps, extra=pending.extra, rows=rows)
+                return h
         if isinstance(pending, Scaled):                  # x += alpha * value
             h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
             ops.add_rmsnorm(x, pending.value, self.weight, h, self.eps, rows=rows, alpha=pending.alpha, cast_first=self.cast_first)
