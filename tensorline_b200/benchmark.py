@@ -568,9 +568,27 @@ def _vutesun_sizes(z):
             "layers": [order[i % 4] for i in range(z["layers"])]}
 
 
+def _dekerax_sizes(z):
+    """Four layers: the delta rule, attention over a window, attention through a latent, the delta rule; one dense feed-forward,
+    three routed ones with a shared expert; the latent as wide as the widest head the tensor-core attention takes."""
+    moe = {"expert": {"ff": z["ff"]}, "kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["ff"]}}
+    delta = {"type": "delta", "mlp": moe, "mixer": {"heads": z["rec_heads"], "kv_heads": z["rec_heads"] // 2, "dim": z["rec_dim"],
+                                                    "vdim": z["rec_vdim"], "conv": 4}}
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": 2 * z["top"] * z["ff"] // 3 // 64 * 64}, "mixer": {
+        "heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"], "scale": z["head"] ** -0.5,
+        "mask": {"size": 1024}}}
+    latent = {"type": "latent_attention", "mlp": moe, "mixer": {
+        "heads": z["heads"], "dim": z["head"], "rot_dim": 64, "rot": {"base": 500000.0, "dims": 64}, "vdim": z["head"],
+        "q_rank": z["width"] // 2, "kv_rank": 192, "scale": (z["head"] + 64) ** -0.5, "mask": {"size": 2048}}}
+    order = [delta, attention, latent, delta]
+    return {"architecture": "Dekerax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "layers": [order[i % 4] for i in range(z["layers"])]}
+
+
 def run_design(a):
     import torch
     from tensorline_b200 import Engine, Qwen2Config
+    from tensorline_b200.config.dekerax import DekeraxConfig
     from tensorline_b200.config.vutesun import VutesunConfig
     if not torch.cuda.is_available():
         print(json.dumps({"impl": "ours", "error": "no CUDA device: this engine runs on the GPU only"}))
@@ -586,6 +604,8 @@ def run_design(a):
         arms = {"vutesun": VutesunConfig.from_dict(_vutesun_sizes(z)),
                 "qwen2": Qwen2Config.from_dict(dict(_sizes(z["layers"], z["width"], z["heads"], z["kv_heads"], dense, 1e-5),
                                                     vocab_size=z["vocab"], eos_token_id=None))}
+        if a.design == "dekerax":                                        # beside the closest design the engine has, at equal sizes
+            arms = {"dekerax": DekeraxConfig.from_dict(_dekerax_sizes(z)), "vutesun": arms["vutesun"]}
         out[tag] = {"sizes": dict(z, dense_intermediate=dense)}
         for name, cfg in arms.items():
             weights = random_weights(cfg, device)
@@ -609,11 +629,12 @@ def run_design(a):
             import gc
             gc.collect(); torch.cuda.empty_cache()
     first = out[sorted(out)[0]]
-    print(json.dumps({"metric": f"decode tok/s of the Vutesun decoder beside Qwen2 at equal layer sizes (bf16, batch {batch}, context {context})",
-                      "value": first["vutesun"][f"decode_b{batch}_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
-                      "ms_per_step": first["vutesun"][f"decode_b{batch}_ms"], "higher_is_better": True, "scaling": "weak",
+    beside = {"vutesun": "Qwen2", "dekerax": "Vutesun"}[a.design]
+    print(json.dumps({"metric": f"decode tok/s of the {a.design.capitalize()} decoder beside {beside} at equal layer sizes (bf16, batch {batch}, context {context})",
+                      "value": first[a.design][f"decode_b{batch}_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+                      "ms_per_step": first[a.design][f"decode_b{batch}_ms"], "higher_is_better": True, "scaling": "weak",
                       "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-                      "config": {"model": "Vutesun and Qwen2 layer sizes of this file, random weights", "global_batch": batch,
+                      "config": {"model": f"{a.design.capitalize()} and {beside} layer sizes of this file, random weights", "global_batch": batch,
                                  "seq_len": context, "parallelism": "single GPU", "peaks": pk_src,
                                  "l2": "inputs larger than L2 (weights, cache and state are re-read from HBM every step)"},
                       "peaks": pk, "designs": out}))
@@ -647,8 +668,9 @@ def main(argv=None):
     ap.add_argument("--timeline", action="store_true",
                     help="print the time line of one captured decode step from the kernels' own stamps (needs TENSORLINE_B200_TRACE=1)")
     ap.add_argument("--no-warm-mix", dest="warm_mix", action="store_false", help="mix: time the first pass (graph capture included)")
-    ap.add_argument("--design", choices=["vutesun"], default=None,
-                    help="instead of the default workload: this design beside Qwen2 at equal layer sizes (prefill, decode, --profile)")
+    ap.add_argument("--design", choices=["vutesun", "dekerax"], default=None,
+                    help="instead of the default workload: this design beside the closest other one at equal layer sizes "
+                         "(vutesun beside Qwen2, dekerax beside vutesun; prefill, decode, --profile)")
     ap.add_argument("--design-size", default="", help="--design: which of the sizes (2k, 4k; commas between them; default all)")
     a = ap.parse_args(argv)
     if a.warmup < 3:

@@ -170,28 +170,30 @@ __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const
         const float* kt = ks + islice * RS;
         const float* qt = qs + islice * RS;
         for (int t = 0; t < n; ++t) {
+            // S^T k is taken of the state before the decay and multiplied by g once (the same sum); the decay and the
+            // write are then one fused multiply-add an element, so a step rounds the state once, not twice
             const float g = gg[t];
             float acc = 0.f;
 #pragma unroll
             for (int r = 0; r < R; r += 4) {
                 const float4 kk = *reinterpret_cast<const float4*>(kt + t * TS + r);
-                S[r] *= g;     acc = fmaf(S[r], kk.x, acc);
-                S[r + 1] *= g; acc = fmaf(S[r + 1], kk.y, acc);
-                S[r + 2] *= g; acc = fmaf(S[r + 2], kk.z, acc);
-                S[r + 3] *= g; acc = fmaf(S[r + 3], kk.w, acc);
+                acc = fmaf(S[r], kk.x, acc);
+                acc = fmaf(S[r + 1], kk.y, acc);
+                acc = fmaf(S[r + 2], kk.z, acc);
+                acc = fmaf(S[r + 3], kk.w, acc);
             }
 #pragma unroll
             for (int o = 1; o < IS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            const float u = gb[t] * (vs[t * DELTA_JS + j] - acc);
+            const float u = gb[t] * (vs[t * DELTA_JS + j] - g * acc);
             float rd = 0.f;
 #pragma unroll
             for (int r = 0; r < R; r += 4) {
                 const float4 kk = *reinterpret_cast<const float4*>(kt + t * TS + r);
                 const float4 qq = *reinterpret_cast<const float4*>(qt + t * TS + r);
-                S[r] = fmaf(kk.x, u, S[r]);         rd = fmaf(S[r], qq.x, rd);
-                S[r + 1] = fmaf(kk.y, u, S[r + 1]); rd = fmaf(S[r + 1], qq.y, rd);
-                S[r + 2] = fmaf(kk.z, u, S[r + 2]); rd = fmaf(S[r + 2], qq.z, rd);
-                S[r + 3] = fmaf(kk.w, u, S[r + 3]); rd = fmaf(S[r + 3], qq.w, rd);
+                S[r] = fmaf(g, S[r], kk.x * u);         rd = fmaf(S[r], qq.x, rd);
+                S[r + 1] = fmaf(g, S[r + 1], kk.y * u); rd = fmaf(S[r + 1], qq.y, rd);
+                S[r + 2] = fmaf(g, S[r + 2], kk.z * u); rd = fmaf(S[r + 2], qq.z, rd);
+                S[r + 3] = fmaf(g, S[r + 3], kk.w * u); rd = fmaf(S[r + 3], qq.w, rd);
             }
 #pragma unroll
             for (int o = 1; o < IS; o <<= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
