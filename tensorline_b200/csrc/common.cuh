@@ -185,6 +185,11 @@ __device__ __forceinline__ float tl_act(float g, int act) {
     return g / (1.0f + expf(-g));
 }
 
+// The gate of a gated product's epilogue: `kind` 1: silu(g) * u as every bfloat16 path computes it, 2: the tanh form of gelu.
+__device__ __forceinline__ float tl_gate_mul(float g, float u, int kind) {
+    return kind == 2 ? tl_gelu_tanh(g) * u : tl_silu_mul(g, u);
+}
+
 // Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while
 // the kernel before it in the stream is still running; its blocks run their set-up and then stop in
 // grid_dependency_wait() until that kernel has finished and its writes are visible.  Every kernel launched

@@ -18,7 +18,8 @@ constexpr int DELTA_C = 16;      // tokens a chunk
 constexpr int DELTA_TOK = 16;    // tokens a block of conv_prep
 
 // ------------------------------------------------------------------ convolution + silu + unit length
-// grid (requests, chunks of DELTA_TOK tokens); a warp a (token, unit), unit = a head of q, k or v.  Output float [T, C].
+// grid (requests, chunks of DELTA_TOK tokens, units / 4); a warp a unit (a head of q, k or v) of the chunk's tokens: a token's
+// taps reach back into rows the warp has just read.  Output float [T, C].
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) conv_prep_kernel(const TA* __restrict__ proj, int stride, const TW* __restrict__ taps_w, int taps,
                                                         const float* __restrict__ conv_state, long long slot_stride,
@@ -32,9 +33,9 @@ __global__ void __launch_bounds__(128) conv_prep_kernel(const TA* __restrict__ p
     const int c0 = t0 + blockIdx.y * DELTA_TOK, c1 = min(t1, c0 + DELTA_TOK);
     if (c0 >= t1) return;
     const float* st = conv_state + (size_t)slots[b] * slot_stride;       // [taps - 1][C], oldest first
-    const int units = 2 * nqk + nv;
-    for (int item = wid; item < (c1 - c0) * units; item += 4) {
-        const int t = c0 + item / units, u = item % units;
+    const int u = blockIdx.z * 4 + wid;                                  // a warp a unit, the chunk's tokens one after the other
+    if (u >= 2 * nqk + nv) return;
+    for (int t = c0; t < c1; ++t) {
         const bool qk = u < 2 * nqk;
         const int width = qk ? d : dv, base = qk ? u * d : 2 * nqk * d + (u - 2 * nqk) * dv;
         const int i = t - t0;                                            // the token's place in the step
@@ -87,8 +88,8 @@ TL_EXPORT int tl_conv_prep(const void* proj, int act_dtype, int stride, const vo
     if (B <= 0 || max_q_len <= 0) return 0;
     if (taps < 1 || (taps > 1 && !conv_state)) return 1;
     const int C = 2 * nqk * d + nv * dv;
-    const dim3 grid(B, (max_q_len + DELTA_TOK - 1) / DELTA_TOK);
-    if (grid.y > 65535) return 1;
+    const dim3 grid(B, (max_q_len + DELTA_TOK - 1) / DELTA_TOK, (2 * nqk + nv + 3) / 4);
+    if (grid.y > 65535 || grid.z > 65535) return 1;
 #define CP(TA, TW) launch_after_wait(conv_prep_kernel<TA, TW>, grid, dim3(128), 0, stream, (const TA*)proj, stride, (const TW*)taps_w, taps, \
         (const float*)conv_state, slot_stride, q_start, slots, out, C, nqk, d, nv, dv, unit_eps, q_scale)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) CP(float, float); else CP(float, bf16); }

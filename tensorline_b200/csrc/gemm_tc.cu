@@ -108,8 +108,9 @@ __device__ __forceinline__ const float* cluster_peer(const float* p, int rank) {
 }
 
 // silu(gate) * up of two accumulator values, each rounded to bfloat16 first (as a stored gate|up product would have been).
-__device__ __forceinline__ float silu_mul_rounded(float gate, float up) {
-    return tl_silu_mul(__bfloat162float(__float2bfloat16_rn(gate)), __bfloat162float(__float2bfloat16_rn(up)));
+// `kind`: 1 silu, 2 the tanh form of gelu.
+__device__ __forceinline__ float silu_mul_rounded(float gate, float up, int kind) {
+    return tl_gate_mul(__bfloat162float(__float2bfloat16_rn(gate)), __bfloat162float(__float2bfloat16_rn(up)), kind);
 }
 
 struct GemmArgs {
@@ -402,7 +403,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int j = 0; j < 8; ++j) {
                         const int t = up_side ? 8 + j : j;
                         const float mine = __uint_as_float(up_side ? r[8 + j] : r[j]), other = hand[t * 64 + f];
-                        res[j] = silu_mul_rounded(up_side ? other : mine, up_side ? mine : other);
+                        res[j] = silu_mul_rounded(up_side ? other : mine, up_side ? mine : other, G.gated);
                     }
                     if (col < (G.RA >> 1)) {
                         bf16* dst = (bf16*)G.out + (size_t)(b0 + c0 + (up_side ? 8 : 0)) * G.ldo + col;

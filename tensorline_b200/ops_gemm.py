@@ -151,13 +151,13 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap
     counters = (st.data_ptr() + 4) if fused_reduce else None
     if normed is None and residual is None:
         _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), ldo, T, N, K, swap, bn, splits,
-                                _ptr(partial), _ptr(st), counters, N_COUNTERS, int(gated), int(use_cluster), _stream()),
+                                _ptr(partial), _ptr(st), counters, N_COUNTERS, _gate_code(gated), int(use_cluster), _stream()),
                name, launches=launches)
     else:
         n = normed
         _check(lib().tl_gemm_tc_normed(
             _ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), ldo, T, N, K, swap, bn, splits,
-            _ptr(partial), _ptr(st), counters, N_COUNTERS, int(gated), int(use_cluster),
+            _ptr(partial), _ptr(st), counters, N_COUNTERS, _gate_code(gated), int(use_cluster),
             _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(ssq),
             _ptr(n.x) if n else None, _ptr(n.ssq) if n else None, n.ssq.shape[1] if n else 0, _ptr(n.weight) if n else None,
             int(n.weight.dtype == torch.float32) if n else 0, float(n.eps) if n else 0.0, _stream()), name, launches=launches)
@@ -204,8 +204,19 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
         raise KernelError("gemm_tc2: out must be [T, N] (gated: [T, N / 2]) of the output type with unit inner stride")
     st = status_word(x.device)
     _check(lib2().tl_gemm_tc2(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), out.stride(0), T, N, K,
-                              int(gated), _ptr(st), int(max_pairs), _stream()), "gemm_tc2" + ("+gated" if gated else ""))
+                              _gate_code(gated), _ptr(st), int(max_pairs), _stream()), "gemm_tc2" + ("+gated" if gated else ""))
     return out
+
+
+def _gate_code(gated) -> int:
+    """`gated` False / True ("silu") / "gelu_tanh" as the kernels take it: 0, 1, 2."""
+    if not gated:
+        return 0
+    if gated is True or gated == "silu":
+        return 1
+    if gated == "gelu_tanh":
+        return 2
+    raise KernelError(f"a gated epilogue applies 'silu' or 'gelu_tanh', not {gated!r}")
 
 
 def can_gate(T: int, N: int, K: int) -> bool:

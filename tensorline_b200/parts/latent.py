@@ -21,6 +21,9 @@ from ..cache import PagedKV
 from .base import POSITION_ENCODINGS, KVCacheView, Part, PartSpec, Rotary, Runtime, TensorSpec, register_mixer
 from .linear import matmul, resolve
 
+# from this many tokens on the bfloat16 engine takes the two products per head to the library (one batched product)
+HEAD_PRODUCT_LIBRARY_MIN_TOKENS = 64
+
 _NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o"}
 
 
@@ -82,14 +85,25 @@ class LatentAttention(Part):
                         table, ctx.page_size, cq, cache.k, write_kv=cache.owner)
         q = resolve(matmul(cq, self.w_uq))
         qa = torch.empty((T, H * d), dtype=act, device=q.device)
-        ops.head_matmul(q, self.w_uk, qa, H, dk, rank, dk + dr, d)
+        self._per_head(q, self.w_uk, qa, dk, rank, dk + dr, d, ctx)
         ops.latent_qrot(q, dk, dr, rotary.inv_freq, rotary.rot, ctx.pos, qa, rank, H)
         o = torch.empty((T, H * d), dtype=act, device=q.device)
         from . import attention_kernels
         attention_kernels.attend(self, qa, o, ctx, KVCacheView(cache.k, cache.k, cache.group, cache.owner), table)
         ov = torch.empty((T, H * self.dv), dtype=act, device=q.device)
-        ops.head_matmul(o, self.w_uv, ov, H, rank, self.dv, d, self.dv)
+        self._per_head(o, self.w_uv, ov, rank, self.dv, d, self.dv, ctx)
         return matmul(ov, self.w_o)
+
+    def _per_head(self, x, w, y, K, N, xs, ys, ctx):
+        """y[t, h, :N] = x[t, h, :K] w[h] with the heads xs (ys) columns apart: the package's kernel, or for long bfloat16 steps
+        one batched library product (as the engine's other long products are the library's)."""
+        T, H = x.shape[0], self.H
+        if x.dtype != torch.bfloat16 or T < HEAD_PRODUCT_LIBRARY_MIN_TOKENS or ctx.graph_max_ctx:
+            ops.head_matmul(x, w, y, H, K, N, xs, ys)
+            return
+        out = torch.matmul(x.view(T, H, xs)[:, :, :K].transpose(0, 1), w)          # [H, T, N]
+        y.view(T, H, ys)[:, :, :N].copy_(out.transpose(0, 1))
+        ops.mark("library product")
 
     def _down(self, h):
         """[Wdq; Wdkv] h as float32 [T, qr + rank + dr]."""

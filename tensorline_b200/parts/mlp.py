@@ -52,17 +52,16 @@ class GatedMLP(Part):
         I = self.intermediate
         if isinstance(h, NormedInput) and h.rows is not None:
             h = h.materialize()
-        silu = self.activation == "silu"                 # the products' own epilogues apply silu only
-        if silu and self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_tc(h.shape[0], 2 * I, self.hidden):
+        if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_tc(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
             if ops_gemm.can_gate(h.shape[0], 2 * I, self.hidden):          # the activation inside the product
-                m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=True)
+                m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=self.activation)
                 return matmul(m, self.w_down, may_defer=True, to_residual=True)
         if isinstance(h, NormedInput):                   # only the few-token products above take the recipe
             h = h.materialize()
-        if silu and self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_pair_product(h.shape[0], 2 * I, self.hidden):
+        if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_pair_product(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
-            m = ops_gemm.gemm_tc2(h, self.w_gate_up, gated=True)          # long steps: pairs of blocks, activation in the epilogue
+            m = ops_gemm.gemm_tc2(h, self.w_gate_up, gated=self.activation)          # long steps: pairs of blocks, activation in the epilogue
             return matmul(m, self.w_down, may_defer=True)
         gu = matmul(h, self.w_gate_up)
         m = torch.empty((h.shape[0], I), dtype=h.dtype, device=h.device)

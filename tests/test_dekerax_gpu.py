@@ -76,6 +76,30 @@ def test_gelu_gate(adt):
     assert_close(out, want, "gelu_tanh(gate) * up", **(F32 if adt == torch.float32 else BF16))
 
 
+@pytest.mark.parametrize("T", [8, 37, 700])
+def test_gelu_gate_in_the_epilogue_of_the_tensor_core_products(T):
+    """Both tcgen05 products with the tanh form of gelu in their epilogue: bit for bit the product, stored in bfloat16,
+    followed by the activation kernel, and the formula in float64."""
+    from tensorline_b200 import ops, ops_gemm
+    I, K = 320, 520
+    x = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
+    g, u = rnd(I, K, seed=2, scale=0.1, dtype=torch.bfloat16), rnd(I, K, seed=3, scale=0.1, dtype=torch.bfloat16)
+    w = torch.stack((g.view(I // 64, 64, K), u.view(I // 64, 64, K)), dim=1).reshape(2 * I, K).contiguous().cuda()
+    if T <= 64:
+        kw = dict(swap=1, bn=16 if T <= 16 else 64, splits=1)
+        got, gu = ops_gemm.gemm_tc(x, w, gated="gelu_tanh", **kw), ops_gemm.gemm_tc(x, w, **kw)
+    else:
+        got, gu = ops_gemm.gemm_tc2(x, w, gated="gelu_tanh"), ops_gemm.gemm_tc2(x, w)
+    ops_gemm.check_status()
+    two_pass = torch.empty(T, I, dtype=torch.bfloat16, device="cuda")
+    ops.silu_mul(gu, two_pass, block=64, act="gelu_tanh")
+    assert torch.equal(got, two_pass)
+    gd, ud = x.double().cpu() @ g.double().T, x.double().cpu() @ u.double().T
+    assert_close(got, plain_model.gelu_tanh(gd) * ud, "gelu_tanh(gate) * up", rtol=3e-2, atol=3e-2)
+    with pytest.raises(ops.KernelError, match="gelu"):
+        ops_gemm.gemm_tc2(x, w, gated="gelu")
+
+
 def _conv_plain(x, w, lens):
     """x [T, C] rows in request order; per request a causal convolution over time, then silu."""
     out, t0 = torch.zeros_like(x), 0
