@@ -86,6 +86,8 @@ def _window(raw, where):
 
 
 def _rotation(raw, where, most) -> Rotation:
+    if raw is None and most == 0:                        # nothing to rotate: the constants may be left out
+        return Rotation(10000.0, 0)
     r = ConfigReader(raw if raw is not None else {}, where)
     rot = Rotation(r.float("base", positive=True), r.int("dims", min=0))
     if rot.dims % 2 or rot.dims > most:
@@ -209,8 +211,9 @@ class DekeraxConfig:
                     mixer["rot"] = {"base": m.rot.base, "dims": m.rot.dims}
             elif l.type == "latent_attention":
                 mixer = mask(m, {"dim": m.dim, "heads": m.heads, "kv_rank": m.kv_rank, "q_rank": m.q_rank,
-                                 "rot": {"base": m.rot.base, "dims": m.rot.dims}, "rot_dim": m.rot_dim, "scale": m.scale,
-                                 "vdim": m.vdim})
+                                 "rot_dim": m.rot_dim, "scale": m.scale, "vdim": m.vdim})
+                if m.rot_dim:
+                    mixer["rot"] = {"base": m.rot.base, "dims": m.rot.dims}
             else:
                 mixer = {"conv": m.conv, "dim": m.dim, "heads": m.heads, "kv_heads": m.kv_heads, "vdim": m.vdim}
             if l.mlp is None:

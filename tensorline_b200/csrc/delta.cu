@@ -16,6 +16,7 @@
 constexpr int DELTA_JS = 16;     // value columns a block
 constexpr int DELTA_C = 16;      // tokens a chunk
 constexpr int DELTA_TOK = 16;    // tokens a block of conv_prep
+constexpr int CONV_KEEP = 8;     // values of a head a lane keeps in registers (heads of up to 256)
 
 // ------------------------------------------------------------------ convolution + silu + unit length
 // grid (requests, chunks of DELTA_TOK tokens, units / 4); a warp a unit (a head of q, k or v) of the chunk's tokens: a token's
@@ -39,9 +40,8 @@ __global__ void __launch_bounds__(128) conv_prep_kernel(const TA* __restrict__ p
         const bool qk = u < 2 * nqk;
         const int width = qk ? d : dv, base = qk ? u * d : 2 * nqk * d + (u - 2 * nqk) * dv;
         const int i = t - t0;                                            // the token's place in the step
-        float ss = 0.f;
-        for (int e = lane; e < width; e += 32) {
-            const int c = base + e;
+        const float unit_scale = u < nqk ? q_scale : 1.0f;
+        auto conv_at = [&](int c) {                                      // convolution and silu of channel c at this token
             float acc = 0.f;
             for (int j = 0; j < taps; ++j) {                             // tap j reads the input taps - 1 - j tokens back
                 const int back = taps - 1 - j, src = i - back;
@@ -49,13 +49,35 @@ __global__ void __launch_bounds__(128) conv_prep_kernel(const TA* __restrict__ p
                                            : st[(size_t)(taps - 1 + src) * C + c];
                 acc = fmaf(to_f<TW>(taps_w[(size_t)c * taps + j]), xin, acc);
             }
-            const float y = acc / (1.0f + expf(-acc));
-            out[(size_t)t * C + c] = y;
+            return acc / (1.0f + expf(-acc));
+        };
+        if (width <= 32 * CONV_KEEP) {                                   // a head's values stay in registers until its length is known
+            float y[CONV_KEEP];
+            float ss = 0.f;
+#pragma unroll
+            for (int m = 0; m < CONV_KEEP; ++m) {
+                const int e = lane + 32 * m;
+                y[m] = e < width ? conv_at(base + e) : 0.f;
+                ss = fmaf(y[m], y[m], ss);
+            }
+            float r = 1.0f;
+            if (qk) r = (1.0f / sqrtf(warp_sum(ss) + unit_eps)) * unit_scale;
+#pragma unroll
+            for (int m = 0; m < CONV_KEEP; ++m) {
+                const int e = lane + 32 * m;
+                if (e < width) out[(size_t)t * C + base + e] = qk ? y[m] * r : y[m];
+            }
+            continue;
+        }
+        float ss = 0.f;                                                  // wider heads: written, then scaled in place
+        for (int e = lane; e < width; e += 32) {
+            const float y = conv_at(base + e);
+            out[(size_t)t * C + base + e] = y;
             ss = fmaf(y, y, ss);
         }
         if (qk) {
             ss = warp_sum(ss);
-            const float r = (1.0f / sqrtf(ss + unit_eps)) * (u < nqk ? q_scale : 1.0f);
+            const float r = (1.0f / sqrtf(ss + unit_eps)) * unit_scale;
             __syncwarp();
             for (int e = lane; e < width; e += 32) out[(size_t)t * C + base + e] *= r;
         }

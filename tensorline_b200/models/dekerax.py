@@ -56,5 +56,5 @@ def describe_dekerax(cfg: DekeraxConfig) -> ModelSpec:
         embedding_prefix="embed", final_norm_prefix="final.norm", head_prefix="head",
         embedding=PartSpec("token_table", {"tensor": ""}), head=PartSpec("linear", {"tensor": ""}),
         embedding_norm=norm, embedding_norm_prefix="embed.norm",
-        stream_rows=cfg.loop.times if cfg.loop is not None and cfg.loop.stop > cfg.loop.start else 0,
+        stream_rows=cfg.loop.times if cfg.loop is not None else 0,       # the table exists whenever the file names a loop
         stream_rows_name="loop.step", stream_rows_eps=eps)

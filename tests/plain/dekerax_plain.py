@@ -90,12 +90,13 @@ def latent_attention(h, w, c, eps, pos=None):
     H, d, dr, dv, R = c["heads"], c["dim"], c["rot_dim"], c["vdim"], c["kv_rank"]
     size = (c.get("mask") or {}).get("size")
     pos = list(range(T)) if pos is None else pos
+    rot = c.get("rot") or {"dims": 0, "base": 1.0}              # nothing to rotate: the constants may be left out
     cq = unit(h @ w["dq"].T, eps) * w["dq.norm"]
     q = (cq @ w["uq"].T).view(T, H, d + dr)
-    q_plain, q_turned = q[..., :d], turn(q[..., d:], pos, c["rot"]["dims"], c["rot"]["base"])
+    q_plain, q_turned = q[..., :d], turn(q[..., d:], pos, rot["dims"], rot["base"])
     down = h @ w["dkv"].T
     lat = unit(down[:, :R], eps) * w["dkv.norm"]
-    shared = turn(down[:, None, R:], pos, c["rot"]["dims"], c["rot"]["base"])[:, 0]
+    shared = turn(down[:, None, R:], pos, rot["dims"], rot["base"])[:, 0]
     k = (lat @ w["uk"].T).view(T, H, d)
     v = (lat @ w["uv"].T).view(T, H, dv)
     o = torch.zeros(T, H, dv, dtype=F64)

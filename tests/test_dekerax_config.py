@@ -31,6 +31,11 @@ def test_the_run_order_is_the_plain_model_s(name):
     assert all(e.reads_cache_of is None for e in spec.run)
     loop = CONFIGS[name].get("loop")
     assert spec.stream_rows == (loop["times"] if loop else 0)
+    empty = copy.deepcopy(CONFIGS[name])
+    empty["loop"] = {"start": 1, "stop": 1, "times": 4}          # a loop over nothing: every layer once, the table still expected
+    cfg = DekeraxConfig.from_dict(empty)
+    assert cfg.run_order() == run_order(empty) == [(i, None) for i in range(len(cfg.layers))]
+    assert tuple(expected_tensors(cfg)["loop.step"].shape) == (4, cfg.width)
     assert len(spec.run) == len(cfg.layers) + ((loop["times"] - 1) * (loop["stop"] - loop["start"]) if loop else 0)
 
 

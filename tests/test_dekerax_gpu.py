@@ -542,11 +542,12 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(model):
         assert st["free_pages"] == st["num_pages"] and st["max_running_seen"] == 3 and (st["graph_replays"] > 0) == graphs
 
 
-@pytest.mark.parametrize("name", ["D3", "D4"])
+@pytest.mark.parametrize("name", ["D3", "D4", "D5"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_further_shapes_of_the_design(name, dtype, tmp_path):
     """The delta rule only (no page group at all, no loop, every expert chosen, grouped heads); a window of one token, a
-    latent without a window, a loop of one pass: whole requests and changing portions against the plain model."""
+    latent without a window, a loop of one pass; sizes that are multiples of nothing much and a latent without a rotated
+    part: whole requests and changing portions against the plain model."""
     folder = write_tiny_dekerax(name, tmp_path / name)
     plain = PlainDekerax(folder)
     V = CONFIGS[name]["vocab"]

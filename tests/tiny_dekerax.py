@@ -57,8 +57,16 @@ D4 = {"architecture": "Dekerax", "vocab": 64, "width": 32, "norm": {"eps": 1e-6}
                                            "kv_rank": 12, "scale": 0.8}, "mlp": _moe(8, 3, 3)},
     {"type": "attention", "mixer": {"heads": 1, "kv_heads": 1, "dim": 48, "vdim": 48, "scale": 0.2, "mask": {"size": 7}}, "mlp": None},
 ]}
-CONFIGS = {"D1": D1, "D2": D2, "D3": D3, "D4": D4}
-PAGE_SIZE = {"D1": 8, "D2": 16, "D3": 4, "D4": 16}
+# sizes that are multiples of nothing much: a width of 52, a vocabulary of 101, odd inner sizes, a latent without a rotated part
+D5 = {"architecture": "Dekerax", "vocab": 101, "width": 52, "norm": {"eps": 1e-5}, "loop": {"start": 0, "stop": 3, "times": 2}, "layers": [
+    {"type": "latent_attention", "mixer": {"heads": 5, "dim": 12, "rot_dim": 6, "rot": {"base": 30.0, "dims": 6}, "vdim": 20, "q_rank": 14,
+                                           "kv_rank": 10, "scale": 0.5, "mask": {"size": 23}}, "mlp": _dense(30)},
+    {"type": "delta", "mixer": {"heads": 3, "kv_heads": 1, "dim": 12, "vdim": 20, "conv": 3}, "mlp": _moe(18, 7, 3, 10)},
+    {"type": "latent_attention", "mixer": {"heads": 2, "dim": 10, "rot_dim": 0, "vdim": 6, "q_rank": 6, "kv_rank": 18, "scale": 0.4,
+                                           "mask": {"size": 40}}, "mlp": None},
+]}
+CONFIGS = {"D1": D1, "D2": D2, "D3": D3, "D4": D4, "D5": D5}
+PAGE_SIZE = {"D1": 8, "D2": 16, "D3": 4, "D4": 16, "D5": 16}
 
 
 def write_tiny_dekerax(name: str, folder=None, seed: int = 0, config: dict | None = None) -> Path:
