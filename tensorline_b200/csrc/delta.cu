@@ -147,7 +147,10 @@ template <int R, int IS> struct DeltaShape {
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
-template <int R, int IS>
+// AHEAD: the next chunk's rows wait in registers while a chunk is worked through (requests of more tokens than a chunk); without
+// it the kernel needs 48 registers instead of 120 and more blocks share an SM, which is what a step of single tokens, all
+// loads and stores of state, wants.  The arithmetic is the same.
+template <int R, int IS, bool AHEAD>
 __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const DeltaArgs A) {
     using Sh = DeltaShape<R, IS>;
     constexpr int NT = Sh::NT, PB = Sh::PB, RS = Sh::RS, TS = Sh::TS, CH = Sh::CH;
@@ -171,25 +174,77 @@ __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const
     const bool live = jcol < A.dv;
     const float neg_rate = -expf(A.A_log[h]), bias = A.dt_bias[h];
     for (int i = tid; i < CH * TS; i += NT) { qs[i] = 0.f; ks[i] = 0.f; }     // rows beyond d stay zero
+    // AHEAD: which elements of a chunk this thread moves never changes, so it is worked out once, and the next chunk's q, k, v
+    // and gate pre-activations wait in registers while this chunk is worked through.
+    constexpr int PF = AHEAD ? CH * R / DELTA_JS : 1;            // q (and k) elements of a chunk a thread fetches (CH R IS / NT)
+    constexpr int PV = AHEAD ? (CH * DELTA_JS + NT - 1) / NT : 1;
+    int g_off[PF], s_off[PF], tok_of[PF], v_goff[PV];
+    unsigned v_ok = 0;
+    float fq[PF], fk[PF], fv[PV], fgb = 0.f, fga = 0.f;
+    if constexpr (AHEAD) {
+#pragma unroll
+        for (int it = 0; it < PF; ++it) {
+            const int idx = tid + it * NT, t = idx / d, e = idx - t * d;
+            tok_of[it] = t < CH ? t : CH;                        // CH: beyond every chunk
+            g_off[it] = t * A.stride + hq * d + e;
+            s_off[it] = t * TS + (e / R) * RS + (e % R);
+        }
+#pragma unroll
+        for (int it = 0; it < PV; ++it) {
+            const int idx = tid + it * NT, t = idx / DELTA_JS, col = z * DELTA_JS + (idx - t * DELTA_JS);
+            v_goff[it] = t * A.stride + A.v_off + h * A.dv + col;
+            if (t < CH && col < A.dv) v_ok |= 1u << it;
+        }
+    }
+    auto fetch = [&](int c0) {
+        const int n = min(CH, t1 - c0);
+        const float* base = A.qkv + (size_t)c0 * A.stride;
+#pragma unroll
+        for (int it = 0; it < PF; ++it)
+            if (tok_of[it] < n) { fq[it] = base[g_off[it] + A.q_off]; fk[it] = base[g_off[it] + A.k_off]; }
+#pragma unroll
+        for (int it = 0; it < PV; ++it)
+            if (((v_ok >> it) & 1u) && (tid + it * NT) / DELTA_JS < n) fv[it] = base[v_goff[it]];
+        if (tid < n) {
+            const float* g = A.gates + (size_t)(c0 + tid) * A.gate_stride;
+            fgb = g[h]; fga = g[A.H + h];
+        }
+    };
+    if constexpr (AHEAD) fetch(t0);
     __syncthreads();
     for (int c0 = t0; c0 < t1; c0 += CH) {
         const int n = min(CH, t1 - c0);
-        for (int i = tid; i < n * d; i += NT) {
-            const int t = i / d, e = i - t * d;
-            const float* row = A.qkv + (size_t)(c0 + t) * A.stride + hq * d + e;
-            qs[t * TS + (e / R) * RS + (e % R)] = row[A.q_off];
-            ks[t * TS + (e / R) * RS + (e % R)] = row[A.k_off];
-        }
-        for (int i = tid; i < n * DELTA_JS; i += NT) {
-            const int t = i / DELTA_JS, col = z * DELTA_JS + (i - t * DELTA_JS);
-            vs[i] = col < A.dv ? A.qkv[(size_t)(c0 + t) * A.stride + A.v_off + h * A.dv + col] : 0.f;
+        if constexpr (AHEAD) {
+#pragma unroll
+            for (int it = 0; it < PF; ++it)
+                if (tok_of[it] < n) { qs[s_off[it]] = fq[it]; ks[s_off[it]] = fk[it]; }
+#pragma unroll
+            for (int it = 0; it < PV; ++it) {
+                const int idx = tid + it * NT;
+                if (idx < n * DELTA_JS) vs[idx] = ((v_ok >> it) & 1u) ? fv[it] : 0.f;
+            }
+        } else {
+            for (int i = tid; i < n * d; i += NT) {
+                const int t = i / d, e = i - t * d;
+                const float* row = A.qkv + (size_t)(c0 + t) * A.stride + hq * d + e;
+                qs[t * TS + (e / R) * RS + (e % R)] = row[A.q_off];
+                ks[t * TS + (e / R) * RS + (e % R)] = row[A.k_off];
+            }
+            for (int i = tid; i < n * DELTA_JS; i += NT) {
+                const int t = i / DELTA_JS, col = z * DELTA_JS + (i - t * DELTA_JS);
+                vs[i] = col < A.dv ? A.qkv[(size_t)(c0 + t) * A.stride + A.v_off + h * A.dv + col] : 0.f;
+            }
+            if (tid < n) {
+                const float* g = A.gates + (size_t)(c0 + tid) * A.gate_stride;
+                fgb = g[h]; fga = g[A.H + h];
+            }
         }
         if (tid < n) {
-            const float* g = A.gates + (size_t)(c0 + tid) * A.gate_stride;
-            gb[tid] = 1.0f / (1.0f + expf(-g[h]));
-            gg[tid] = expf(neg_rate * softplus_f(g[A.H + h] + bias));
+            gb[tid] = 1.0f / (1.0f + expf(-fgb));
+            gg[tid] = expf(neg_rate * softplus_f(fga + bias));
         }
         __syncthreads();
+        if (AHEAD && c0 + CH < t1) fetch(c0 + CH);
         const float* kt = ks + islice * RS;
         const float* qt = qs + islice * RS;
         for (int t = 0; t < n; ++t) {
@@ -244,17 +299,21 @@ TL_EXPORT int tl_delta_columns() { return DELTA_JS; }
 
 TL_EXPORT int tl_delta_scan(const float* qkv, int stride, int q_off, int k_off, int v_off, const float* gates, int gate_stride,
                             const float* A_log, const float* dt_bias, float* state, long long slot_stride, const int* q_start,
-                            const int* slots, float* out, int B, int H, int nqk, int d, int dv, cudaStream_t stream) {
+                            const int* slots, float* out, int B, int H, int nqk, int d, int dv, int max_q_len, cudaStream_t stream) {
     if (B <= 0 || H <= 0) return 0;
     if (H > 65535 || nqk < 1 || H % nqk) return 1;
     const DeltaArgs A{qkv, stride, q_off, k_off, v_off, gates, gate_stride, A_log, dt_bias, state, slot_stride, q_start, slots, out,
                       H, nqk, d, dv};
     const dim3 grid(B, H, (dv + DELTA_JS - 1) / DELTA_JS);
+#define DS(R_, IS_) (max_q_len > DeltaShape<R_, IS_>::CH \
+        ? launch_after_wait(delta_scan_kernel<R_, IS_, true>, grid, dim3(DeltaShape<R_, IS_>::NT), 0, stream, A) \
+        : launch_after_wait(delta_scan_kernel<R_, IS_, false>, grid, dim3(DeltaShape<R_, IS_>::NT), 0, stream, A))
     switch (delta_shape(d)) {
-        case 0: return launch_after_wait(delta_scan_kernel<4, 8>, grid, dim3(DeltaShape<4, 8>::NT), 0, stream, A);
-        case 1: return launch_after_wait(delta_scan_kernel<8, 8>, grid, dim3(DeltaShape<8, 8>::NT), 0, stream, A);
-        case 2: return launch_after_wait(delta_scan_kernel<8, 16>, grid, dim3(DeltaShape<8, 16>::NT), 0, stream, A);
-        case 3: return launch_after_wait(delta_scan_kernel<8, 32>, grid, dim3(DeltaShape<8, 32>::NT), 0, stream, A);
+        case 0: return DS(4, 8);
+        case 1: return DS(8, 8);
+        case 2: return DS(8, 16);
+        case 3: return DS(8, 32);
     }
+#undef DS
     return 1;
 }

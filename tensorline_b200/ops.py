@@ -44,7 +44,7 @@ _SIGNATURES = {
     "tl_relu_square": [_P, _I, ctypes.c_longlong, _P],
     "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _P],
     "tl_conv_prep": [_P, _I, _I, _P, _I, _I, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
-    "tl_delta_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "tl_delta_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "tl_delta_state_floats": [_I],
     "tl_delta_columns": [],
     "tl_latent_prep": [_P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -721,11 +721,13 @@ def conv_prep(proj: torch.Tensor, taps_w: torch.Tensor, conv_state: torch.Tensor
 
 
 def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
-               q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, *, B: int, H: int, nqk: int, d: int, dv: int) -> None:
+               q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, *, B: int, H: int, nqk: int, d: int, dv: int,
+               max_q_len: int | None = None) -> None:
     """Per (request, head), tokens in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
     beta = sigmoid(gates[t, h]) and g = exp(-exp(A_log[h]) softplus(gates[t, H + h] + dt_bias[h])).  qkv float32 [T, C] as
     `conv_prep` leaves it (q [nqk, d], k [nqk, d], v [H, dv]; head h reads q/k head h // (H / nqk)); the state is read from
-    and left in `state[slot]` (float32, `delta_state_floats` per head and column slice); out float32 [T, H dv]."""
+    and left in `state[slot]` (float32, `delta_state_floats` per head and column slice); out float32 [T, H dv].  `max_q_len`: the most tokens a request brings
+    (None: as many as the step has); it only picks between two forms of the kernel that give the same bits."""
     T = qkv.shape[0]
     C = 2 * nqk * d + H * dv
     if qkv.dtype != torch.float32 or qkv.shape != (T, C) or out.dtype != torch.float32 or out.shape != (T, H * dv):
@@ -740,7 +742,8 @@ def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, A_log: torch.Tensor, dt_b
     if state.dtype != torch.float32 or state[0].numel() != per_slot:
         raise KernelError(f"delta_scan: a slot holds {state[0].numel()} floats, these sizes need {per_slot}")
     _check(core().tl_delta_scan(_ptr(qkv), C, 0, nqk * d, 2 * nqk * d, _ptr(gates), gates.stride(0), _ptr(A_log), _ptr(dt_bias),
-                                _ptr(state), per_slot, _ptr(q_start), _ptr(slots), _ptr(out), int(B), H, nqk, d, dv, _stream()),
+                                _ptr(state), per_slot, _ptr(q_start), _ptr(slots), _ptr(out), int(B), H, nqk, d, dv,
+                                int(T if max_q_len is None else max_q_len), _stream()),
            "delta_scan")
 
 

@@ -89,7 +89,7 @@ class GatedDelta(Part):
                       nv=H, dv=dv, unit_eps=self.unit_eps, q_scale=d ** -0.5)
         o = torch.empty((T, H * dv), dtype=torch.float32, device=h.device)
         ops.delta_scan(qkv, gates, self.A_log, self.dt_bias, cache["memory"].state, ctx.q_start, ctx.slots, o, B=ctx.B, H=H,
-                       nqk=nqk, d=d, dv=dv)
+                       nqk=nqk, d=d, dv=dv, max_q_len=ctx.max_q_len)
         y = torch.empty((T, H * dv), dtype=h.dtype, device=h.device)
         ops.head_norm_gate(o, y, H, dv, self.eps, weight=self.head_weight, gate=proj, gate_off=C, act="silu")
         return matmul(y, self.w_o)
