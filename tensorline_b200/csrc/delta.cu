@@ -15,7 +15,7 @@
 
 constexpr int DELTA_JS = 16;     // value columns a block
 constexpr int DELTA_C = 16;      // tokens a chunk
-constexpr int DELTA_TOK = 16;    // tokens a block of conv_prep
+constexpr int DELTA_TOK = 4;     // tokens a warp of conv_prep takes one after the other
 constexpr int CONV_KEEP = 8;     // values of a head a lane keeps in registers (heads of up to 256)
 
 // ------------------------------------------------------------------ convolution + silu + unit length

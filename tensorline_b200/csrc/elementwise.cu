@@ -337,14 +337,127 @@ __global__ void __launch_bounds__(256) post_norm_add_norm_kernel(float* __restri
     }
 }
 
+// The fast path: H a multiple of 4; a thread keeps its NV chunks of 4 values of x and a in registers, so every load of the
+// row is in flight at once and x, a are read exactly once.  A launch of few rows (a decode step) reads the weights, which
+// are nobody's output, before the wait for the kernel in front.
+template <typename TA, typename TW, int NV>
+__global__ void post_norm_add_norm_vec_kernel(float* __restrict__ x, const TA* __restrict__ a, const TW* __restrict__ w_post,
+                                              const float* __restrict__ extra, const TW* __restrict__ w_pre, TA* __restrict__ out,
+                                              const int* __restrict__ rows, int H, float eps, int write_x) {
+    __shared__ float red[33];
+    const int i = blockIdx.x, nvec = H >> 2;
+    float v[NV][4], av[NV][4], wv[NV][4];
+    const bool early = gridDim.x <= 128;
+    if (early && a) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) Vec4<TW>::load(w_post + 4 * c, wv[k]);
+        }
+    }
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const size_t src = (size_t)(rows ? rows[i] : i) * H;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) {
+            Vec4<float>::load(x + src + 4 * c, v[k]);
+            if (a) {
+                Vec4<TA>::load(a + src + 4 * c, av[k]);
+                if (!early) Vec4<TW>::load(w_post + 4 * c, wv[k]);
+            }
+        }
+    }
+    if (a) {
+        float sa = 0.f;
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+            if (threadIdx.x + k * blockDim.x < nvec)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sa = fmaf(av[k][e], av[k][e], sa);
+        sa = block_sum(sa, red);
+        const float ra = 1.0f / sqrtf(sa / (float)H + eps);
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[k][e] += av[k][e] * ra * wv[k][e];
+    }
+    if (extra) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) {
+                float ev[4];
+                Vec4<float>::load(extra + 4 * c, ev);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[k][e] += ev[e];
+            }
+        }
+    }
+    if (write_x && (a || extra)) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) Vec4<float>::store(x + src + 4 * c, v[k]);
+        }
+    }
+    if (!out) return;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {                           // the second norm's weights: the first one's are done with
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) Vec4<TW>::load(w_pre + 4 * c, wv[k]);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+        if (threadIdx.x + k * blockDim.x < nvec)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(v[k][e], v[k][e], ss);
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = v[k][e] * rstd * wv[k][e];
+            Vec4<TA>::store(out + (size_t)i * H + 4 * c, o);
+        }
+    }
+}
+
+template <typename TA, typename TW>
+static int launch_post_norm(void* x, const void* a, const void* w_post, const float* extra, const void* w_pre, void* out,
+                            const int* rows, int R, int H, float eps, int write_x, cudaStream_t stream) {
+    const int nvec = H >> 2;
+    const bool vec = (H & 3) == 0 && nvec <= 4096 &&
+                     ((((uintptr_t)x | (uintptr_t)a | (uintptr_t)w_post | (uintptr_t)w_pre | (uintptr_t)out | (uintptr_t)extra) & 15) == 0);
+#define PNV(NV) { int th = ((nvec + NV - 1) / NV + 31) / 32 * 32; \
+        return launch_after_wait(post_norm_add_norm_vec_kernel<TA, TW, NV>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)a, \
+                                 (const TW*)w_post, extra, (const TW*)w_pre, (TA*)out, rows, H, eps, write_x); }
+    if (vec) {
+        if (nvec <= 1024) PNV(1)
+        else if (nvec <= 2048) PNV(2)
+        else PNV(4)
+    }
+#undef PNV
+    return launch_after_wait(post_norm_add_norm_kernel<TA, TW>, dim3(R), dim3(256), 0, stream, (float*)x, (const TA*)a,
+                             (const TW*)w_post, extra, (const TW*)w_pre, (TA*)out, rows, H, eps, write_x);
+}
+
 TL_EXPORT int tl_post_norm_add_norm(void* x, const void* a, const void* w_post, const float* extra, const void* w_pre, int w_dtype,
                                     void* out, int act_dtype, const int* rows, int R, int H, float eps, int write_x,
                                     cudaStream_t stream) {
     if (R <= 0) return 0;
-#define PN(TA, TW) launch_after_wait(post_norm_add_norm_kernel<TA, TW>, dim3(R), dim3(256), 0, stream, (float*)x, (const TA*)a, \
-        (const TW*)w_post, extra, (const TW*)w_pre, (TA*)out, rows, H, eps, write_x)
-    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) PN(float, float); else PN(float, bf16); }
-    else { if (w_dtype == TL_F32) PN(bf16, float); else PN(bf16, bf16); }
-#undef PN
-    return tl_launch_status();
+    int e;
+    if (act_dtype == TL_F32) {
+        e = w_dtype == TL_F32 ? launch_post_norm<float, float>(x, a, w_post, extra, w_pre, out, rows, R, H, eps, write_x, stream)
+                              : launch_post_norm<float, bf16>(x, a, w_post, extra, w_pre, out, rows, R, H, eps, write_x, stream);
+    } else {
+        e = w_dtype == TL_F32 ? launch_post_norm<bf16, float>(x, a, w_post, extra, w_pre, out, rows, R, H, eps, write_x, stream)
+                              : launch_post_norm<bf16, bf16>(x, a, w_post, extra, w_pre, out, rows, R, H, eps, write_x, stream);
+    }
+    return e ? e : tl_launch_status();
 }

@@ -100,14 +100,15 @@ TL_EXPORT int tl_latent_qrot(const void* q, int dk, int dr, const float* inv_fre
 }
 
 // y[t, h, n] = sum_k x[t, h, k] w[h, k, n];  x rows `ldx` apart, heads `hx` apart (y: ldy, hy).  grid (token tiles, heads,
-// column tiles of 128); a thread a column, HM_T tokens at a time with their x rows in shared memory as float, so a weight is
-// loaded once for HM_T sums.  Each sum is one chain over k in order: a row's result does not depend on the step's other rows.
+// column tiles of the block's width: 128, or 32 for steps of few tokens so that they still fill SMs); a thread a column, HM_T
+// tokens at a time with their x rows in shared memory as float, so a weight is loaded once for HM_T sums; eight weights' loads
+// are in flight at a time.  Each sum is one chain over k in order: a row's result does not depend on the step's other rows.
 constexpr int HM_T = 8;
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) head_matmul_kernel(const TA* __restrict__ x, int ldx, int hx, const TW* __restrict__ w,
                                                           TA* __restrict__ y, int ldy, int hy, int T, int K, int N) {
     extern __shared__ float xs[];                        // [HM_T][K]
-    const int t0 = blockIdx.x * HM_T, h = blockIdx.y, n = blockIdx.z * 128 + threadIdx.x;
+    const int t0 = blockIdx.x * HM_T, h = blockIdx.y, n = blockIdx.z * blockDim.x + threadIdx.x;
     grid_dependency_wait();
     grid_dependency_trigger();
     const int nt = min(HM_T, T - t0);
@@ -121,7 +122,19 @@ __global__ void __launch_bounds__(128) head_matmul_kernel(const TA* __restrict__
 #pragma unroll
     for (int t = 0; t < HM_T; ++t) acc[t] = 0.f;
     const TW* wh = w + (size_t)h * K * N + n;
-    for (int k = 0; k < K; ++k) {
+    int k = 0;
+    for (; k + 8 <= K; k += 8) {
+        TW w8[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) w8[u] = wh[(size_t)(k + u) * N];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float wv = to_f<TW>(w8[u]);
+#pragma unroll
+            for (int t = 0; t < HM_T; ++t) if (t < nt) acc[t] = fmaf(xs[t * K + k + u], wv, acc[t]);
+        }
+    }
+    for (; k < K; ++k) {
         const float wv = to_f<TW>(wh[(size_t)k * N]);
 #pragma unroll
         for (int t = 0; t < HM_T; ++t) if (t < nt) acc[t] = fmaf(xs[t * K + k], wv, acc[t]);
@@ -134,9 +147,10 @@ TL_EXPORT int tl_head_matmul(const void* x, int ldx, int hx, const void* w, int 
                              int N, int act_dtype, cudaStream_t stream) {
     if (T <= 0 || H <= 0 || N <= 0) return 0;
     const size_t smem = (size_t)HM_T * K * sizeof(float);
-    if (smem > 48 * 1024 || H > 65535 || (N + 127) / 128 > 65535) return 1;
-    const dim3 grid((T + HM_T - 1) / HM_T, H, (N + 127) / 128);
-#define HM(TA, TW) launch_after_wait(head_matmul_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)x, ldx, hx, (const TW*)w, (TA*)y, ldy, hy, T, K, N)
+    const int width = T <= 2 * HM_T ? 32 : 128;          // columns a block
+    if (smem > 48 * 1024 || H > 65535 || (N + width - 1) / width > 65535) return 1;
+    const dim3 grid((T + HM_T - 1) / HM_T, H, (N + width - 1) / width);
+#define HM(TA, TW) launch_after_wait(head_matmul_kernel<TA, TW>, grid, dim3(width), smem, stream, (const TA*)x, ldx, hx, (const TW*)w, (TA*)y, ldy, hy, T, K, N)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) HM(float, float); else HM(float, bf16); }
     else { if (w_dtype == TL_F32) HM(bf16, float); else HM(bf16, bf16); }
 #undef HM
