@@ -100,15 +100,18 @@ TL_EXPORT int tl_latent_qrot(const void* q, int dk, int dr, const float* inv_fre
 }
 
 // y[t, h, n] = sum_k x[t, h, k] w[h, k, n];  x rows `ldx` apart, heads `hx` apart (y: ldy, hy).  grid (token tiles, heads,
-// column tiles of the block's width: 128, or 32 for steps of few tokens so that they still fill SMs); a thread a column, HM_T
-// tokens at a time with their x rows in shared memory as float, so a weight is loaded once for HM_T sums; eight weights' loads
-// are in flight at a time.  Each sum is one chain over k in order: a row's result does not depend on the step's other rows.
+// column tiles of 32); a block is 32 columns x 4 quarters of k: a thread sums its quarter of k in order for HM_T tokens (their x
+// rows sit in shared memory as float, a weight is loaded once for HM_T sums, eight weights' loads are in flight at a time), and
+// the four quarters are added in order.  Every output is one fixed chain of additions: a row's result does not depend on the
+// step's other rows or on how many there are.
 constexpr int HM_T = 8;
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) head_matmul_kernel(const TA* __restrict__ x, int ldx, int hx, const TW* __restrict__ w,
                                                           TA* __restrict__ y, int ldy, int hy, int T, int K, int N) {
-    extern __shared__ float xs[];                        // [HM_T][K]
-    const int t0 = blockIdx.x * HM_T, h = blockIdx.y, n = blockIdx.z * blockDim.x + threadIdx.x;
+    extern __shared__ float xs[];                        // [HM_T][K], then the quarters' sums [4][HM_T][32]
+    float* part = xs + HM_T * K;
+    const int col = threadIdx.x & 31, quarter = threadIdx.x >> 5;
+    const int t0 = blockIdx.x * HM_T, h = blockIdx.y, n = blockIdx.z * 32 + col;
     grid_dependency_wait();
     grid_dependency_trigger();
     const int nt = min(HM_T, T - t0);
@@ -117,40 +120,52 @@ __global__ void __launch_bounds__(128) head_matmul_kernel(const TA* __restrict__
         xs[i] = to_f<TA>(x[(size_t)(t0 + t) * ldx + (size_t)h * hx + k]);
     }
     __syncthreads();
-    if (n >= N) return;
     float acc[HM_T];
 #pragma unroll
     for (int t = 0; t < HM_T; ++t) acc[t] = 0.f;
-    const TW* wh = w + (size_t)h * K * N + n;
-    int k = 0;
-    for (; k + 8 <= K; k += 8) {
-        TW w8[8];
+    const int per = (K + 3) / 4, k1 = min(K, (quarter + 1) * per);
+    int k = quarter * per;
+    if (n < N) {
+        const TW* wh = w + (size_t)h * K * N + n;
+        for (; k + 8 <= k1; k += 8) {
+            TW w8[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) w8[u] = wh[(size_t)(k + u) * N];
+            for (int u = 0; u < 8; ++u) w8[u] = wh[(size_t)(k + u) * N];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const float wv = to_f<TW>(w8[u]);
+            for (int u = 0; u < 8; ++u) {
+                const float wv = to_f<TW>(w8[u]);
 #pragma unroll
-            for (int t = 0; t < HM_T; ++t) if (t < nt) acc[t] = fmaf(xs[t * K + k + u], wv, acc[t]);
+                for (int t = 0; t < HM_T; ++t) if (t < nt) acc[t] = fmaf(xs[t * K + k + u], wv, acc[t]);
+            }
+        }
+        for (; k < k1; ++k) {
+            const float wv = to_f<TW>(wh[(size_t)k * N]);
+#pragma unroll
+            for (int t = 0; t < HM_T; ++t) if (t < nt) acc[t] = fmaf(xs[t * K + k], wv, acc[t]);
         }
     }
-    for (; k < K; ++k) {
-        const float wv = to_f<TW>(wh[(size_t)k * N]);
 #pragma unroll
-        for (int t = 0; t < HM_T; ++t) if (t < nt) acc[t] = fmaf(xs[t * K + k], wv, acc[t]);
+    for (int t = 0; t < HM_T; ++t) part[(quarter * HM_T + t) * 32 + col] = acc[t];
+    __syncthreads();
+    if (quarter == 0 && n < N) {
+#pragma unroll
+        for (int t = 0; t < HM_T; ++t) {
+            if (t < nt) {
+                const float v = ((part[t * 32 + col] + part[(HM_T + t) * 32 + col]) + part[(2 * HM_T + t) * 32 + col]) +
+                                part[(3 * HM_T + t) * 32 + col];
+                y[(size_t)(t0 + t) * ldy + (size_t)h * hy + n] = from_f<TA>(v);
+            }
+        }
     }
-#pragma unroll
-    for (int t = 0; t < HM_T; ++t) if (t < nt) y[(size_t)(t0 + t) * ldy + (size_t)h * hy + n] = from_f<TA>(acc[t]);
 }
 
 TL_EXPORT int tl_head_matmul(const void* x, int ldx, int hx, const void* w, int w_dtype, void* y, int ldy, int hy, int T, int H, int K,
                              int N, int act_dtype, cudaStream_t stream) {
     if (T <= 0 || H <= 0 || N <= 0) return 0;
-    const size_t smem = (size_t)HM_T * K * sizeof(float);
-    const int width = T <= 2 * HM_T ? 32 : 128;          // columns a block
-    if (smem > 48 * 1024 || H > 65535 || (N + width - 1) / width > 65535) return 1;
-    const dim3 grid((T + HM_T - 1) / HM_T, H, (N + width - 1) / width);
-#define HM(TA, TW) launch_after_wait(head_matmul_kernel<TA, TW>, grid, dim3(width), smem, stream, (const TA*)x, ldx, hx, (const TW*)w, (TA*)y, ldy, hy, T, K, N)
+    const size_t smem = ((size_t)HM_T * K + 4 * HM_T * 32) * sizeof(float);
+    if (smem > 48 * 1024 || H > 65535 || (N + 31) / 32 > 65535) return 1;
+    const dim3 grid((T + HM_T - 1) / HM_T, H, (N + 31) / 32);
+#define HM(TA, TW) launch_after_wait(head_matmul_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)x, ldx, hx, (const TW*)w, (TA*)y, ldy, hy, T, K, N)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) HM(float, float); else HM(float, bf16); }
     else { if (w_dtype == TL_F32) HM(bf16, float); else HM(bf16, bf16); }
 #undef HM

@@ -40,7 +40,7 @@ class GatedDelta(Part):
         self.hidden, self.H, self.nqk, self.d, self.dv, self.taps, self.eps = hidden, num_heads, num_qk_heads, head_dim, v_head_dim, taps, norm_eps
         self.C = 2 * num_qk_heads * head_dim + num_heads * v_head_dim          # channels that pass the convolution
         self.names = {**_NAMES, **(names or {})}
-        self.w_in = self.w_gates = self.w_o = self.taps_w = self.A_log = self.dt_bias = self.head_weight = None
+        self.w_in = self.w_o = self.taps_w = self.A_log = self.dt_bias = self.head_weight = None
 
     def _state_floats(self) -> int:
         """As `ops.delta_state_floats` says on the device: R rows in each of IS x 16 threads."""
@@ -65,8 +65,8 @@ class GatedDelta(Part):
 
     def bind(self, weights, prefix):
         n = {k: f"{prefix}.{v}" for k, v in self.names.items()}
-        self.w_in = self._compute_copy(torch.cat([weights[n[k]] for k in ("q", "k", "v", "g")], dim=0))
-        self.w_gates = torch.cat([weights[n["b"]], weights[n["a"]]], dim=0).contiguous()       # stored type; float32 product
+        # one stacked projection: q | k | v | gate | b | a; its float32 accumulators are what the recurrence reads
+        self.w_in = self._compute_copy(torch.cat([weights[n[k]] for k in ("q", "k", "v", "g", "b", "a")], dim=0))
         self.taps_w = torch.cat([weights[n[k]] for k in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
         self.A_log = weights[n["A_log"]].float().contiguous()
         self.dt_bias = weights[n["dt_bias"]].float().contiguous()
@@ -80,9 +80,8 @@ class GatedDelta(Part):
         H, nqk, d, dv, C = self.H, self.nqk, self.d, self.dv, self.C
         h = resolve(h)
         T = h.shape[0]
-        proj = resolve(matmul(h, self.w_in, out_dtype=torch.float32))           # q | k | v | gate, float32 accumulators
-        gates = torch.empty((T, 2 * H), dtype=torch.float32, device=h.device)
-        ops.small_proj(h, self.w_gates, None, gates)
+        proj = resolve(matmul(h, self.w_in, out_dtype=torch.float32))           # q | k | v | gate | b | a, float32 accumulators
+        gates = proj[:, C + H * dv:]                                            # the write strengths' and decays' pre-activations
         qkv = torch.empty((T, C), dtype=torch.float32, device=h.device)
         inputs = cache["inputs"].state if self.taps > 1 else None
         ops.conv_prep(proj, self.taps_w, inputs, ctx.q_start, ctx.slots, qkv, B=ctx.B, max_q_len=ctx.max_q_len, nqk=nqk, d=d,

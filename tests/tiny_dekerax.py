@@ -69,10 +69,10 @@ CONFIGS = {"D1": D1, "D2": D2, "D3": D3, "D4": D4, "D5": D5}
 PAGE_SIZE = {"D1": 8, "D2": 16, "D3": 4, "D4": 16, "D5": 16}
 
 
-def write_tiny_dekerax(name: str, folder=None, seed: int = 0, config: dict | None = None) -> Path:
+def write_tiny_dekerax(name: str, folder=None, seed: int = 0, config: dict | None = None, std: float = 0.12) -> Path:
     cfg = DekeraxConfig.from_dict(config or CONFIGS[name])
     folder = Path(folder) if folder is not None else Path(tempfile.mkdtemp(prefix=f"tiny_{name}_"))
-    write_random_model(folder, cfg, expected_tensors(cfg), seed=seed, std=0.12, norm_std=0.1)
+    write_random_model(folder, cfg, expected_tensors(cfg), seed=seed, std=std, norm_std=0.1)
     f = SafetensorsFile(folder / "model.safetensors")
     tensors = {n: f.tensor(n).clone() for n in f.names()}
     f.close()
