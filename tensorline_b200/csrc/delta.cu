@@ -84,6 +84,60 @@ __global__ void __launch_bounds__(128) conv_prep_kernel(const TA* __restrict__ p
     }
 }
 
+// The same for steps of many tokens: a block a (request, chunk of `tt` tokens, head); the chunk's rows of the head, with the
+// taps - 1 rows in front of them, and the head's weights are brought into shared memory once (all loads in flight), then a warp
+// a token.  The arithmetic of an output is conv_prep_kernel's, operation for operation, so both give the same bits.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256) conv_prep_tile_kernel(const TA* __restrict__ proj, int stride, const TW* __restrict__ taps_w, int taps,
+                                                             const float* __restrict__ conv_state, long long slot_stride,
+                                                             const int* __restrict__ q_start, const int* __restrict__ slots,
+                                                             float* __restrict__ out, int C, int nqk, int d, int nv, int dv,
+                                                             float unit_eps, float q_scale, int tt) {
+    extern __shared__ float sm[];                        // rows [tt + taps - 1][width], then weights [width][taps]
+    const int b = blockIdx.x, u = blockIdx.z, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    const int c0 = t0 + blockIdx.y * tt, c1 = min(t1, c0 + tt);
+    if (c0 >= t1) return;
+    const bool qk = u < 2 * nqk;
+    const int width = qk ? d : dv, base = qk ? u * d : 2 * nqk * d + (u - 2 * nqk) * dv;
+    const float* st = conv_state + (size_t)slots[b] * slot_stride;
+    float* ws = sm + (size_t)(tt + taps - 1) * width;
+    const int nrows = (c1 - c0) + taps - 1, first = (c0 - t0) - (taps - 1);       // place in the step of the tile's first row
+    for (int i = threadIdx.x; i < nrows * width; i += blockDim.x) {
+        const int r = i / width, e = i - r * width, src = first + r;
+        sm[i] = src >= 0 ? to_f<TA>(proj[(size_t)(t0 + src) * stride + base + e]) : st[(size_t)(taps - 1 + src) * C + base + e];
+    }
+    for (int i = threadIdx.x; i < width * taps; i += blockDim.x) ws[i] = to_f<TW>(taps_w[(size_t)base * taps + i]);
+    __syncthreads();
+    const float unit_scale = u < nqk ? q_scale : 1.0f;
+    for (int t = c0 + wid; t < c1; t += 8) {
+        const float* rows = sm + (size_t)(t - c0) * width;               // the row taps - 1 tokens back
+        float y[CONV_KEEP];
+        float ss = 0.f;
+#pragma unroll
+        for (int m = 0; m < CONV_KEEP; ++m) {
+            const int e = lane + 32 * m;
+            float v = 0.f;
+            if (e < width) {
+                float acc = 0.f;
+                for (int j = 0; j < taps; ++j) acc = fmaf(ws[e * taps + j], rows[(size_t)j * width + e], acc);
+                v = acc / (1.0f + expf(-acc));
+            }
+            y[m] = v;
+            ss = fmaf(v, v, ss);
+        }
+        float r = 1.0f;
+        if (qk) r = (1.0f / sqrtf(warp_sum(ss) + unit_eps)) * unit_scale;
+#pragma unroll
+        for (int m = 0; m < CONV_KEEP; ++m) {
+            const int e = lane + 32 * m;
+            if (e < width) out[(size_t)t * C + base + e] = qk ? y[m] * r : y[m];
+        }
+    }
+}
+
 // The slot's inputs after the step: the last taps - 1 of (what the slot held, then the step's inputs).  A thread a channel;
 // going from the oldest place on, every place reads a place behind it or the step's rows, so nothing is read after it
 // was overwritten.
@@ -110,13 +164,29 @@ TL_EXPORT int tl_conv_prep(const void* proj, int act_dtype, int stride, const vo
     if (B <= 0 || max_q_len <= 0) return 0;
     if (taps < 1 || (taps > 1 && !conv_state)) return 1;
     const int C = 2 * nqk * d + nv * dv;
-    const dim3 grid(B, (max_q_len + DELTA_TOK - 1) / DELTA_TOK, (2 * nqk + nv + 3) / 4);
-    if (grid.y > 65535 || grid.z > 65535) return 1;
+    // steps of many tokens with heads of up to 32 * CONV_KEEP: the tile kernel, as many tokens a block as 40 KB of rows hold
+    const int widest = d > dv ? d : dv;
+    int tt = (int)(40 * 1024 / sizeof(float)) / widest - (taps - 1);
+    tt = tt > 32 ? 32 : tt;
+    if (max_q_len >= 16 && widest <= 32 * CONV_KEEP && tt >= 8 && 2 * nqk + nv <= 65535) {
+        const dim3 grid(B, (max_q_len + tt - 1) / tt, 2 * nqk + nv);
+        if (grid.y > 65535) return 1;
+        const size_t smem = ((size_t)(tt + taps - 1) * widest + (size_t)widest * taps) * sizeof(float);
+        if (smem > 48 * 1024) return 1;
+#define CT(TA, TW) launch_after_wait(conv_prep_tile_kernel<TA, TW>, grid, dim3(256), smem, stream, (const TA*)proj, stride, (const TW*)taps_w, taps, \
+        (const float*)conv_state, slot_stride, q_start, slots, out, C, nqk, d, nv, dv, unit_eps, q_scale, tt)
+        if (act_dtype == TL_F32) { if (w_dtype == TL_F32) CT(float, float); else CT(float, bf16); }
+        else { if (w_dtype == TL_F32) CT(bf16, float); else CT(bf16, bf16); }
+#undef CT
+    } else {
+        const dim3 grid(B, (max_q_len + DELTA_TOK - 1) / DELTA_TOK, (2 * nqk + nv + 3) / 4);
+        if (grid.y > 65535 || grid.z > 65535) return 1;
 #define CP(TA, TW) launch_after_wait(conv_prep_kernel<TA, TW>, grid, dim3(128), 0, stream, (const TA*)proj, stride, (const TW*)taps_w, taps, \
         (const float*)conv_state, slot_stride, q_start, slots, out, C, nqk, d, nv, dv, unit_eps, q_scale)
-    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) CP(float, float); else CP(float, bf16); }
-    else { if (w_dtype == TL_F32) CP(bf16, float); else CP(bf16, bf16); }
+        if (act_dtype == TL_F32) { if (w_dtype == TL_F32) CP(float, float); else CP(float, bf16); }
+        else { if (w_dtype == TL_F32) CP(bf16, float); else CP(bf16, bf16); }
 #undef CP
+    }
     int e = tl_launch_status();
     if (e || taps == 1) return e;
     const dim3 kgrid(B, (C + 255) / 256 < 64 ? (C + 255) / 256 : 64);
