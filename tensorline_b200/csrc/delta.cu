@@ -105,9 +105,15 @@ __global__ void __launch_bounds__(256) conv_prep_tile_kernel(const TA* __restric
     const float* st = conv_state + (size_t)slots[b] * slot_stride;
     float* ws = sm + (size_t)(tt + taps - 1) * width;
     const int nrows = (c1 - c0) + taps - 1, first = (c0 - t0) - (taps - 1);       // place in the step of the tile's first row
-    for (int i = threadIdx.x; i < nrows * width; i += blockDim.x) {
-        const int r = i / width, e = i - r * width, src = first + r;
-        sm[i] = src >= 0 ? to_f<TA>(proj[(size_t)(t0 + src) * stride + base + e]) : st[(size_t)(taps - 1 + src) * C + base + e];
+    int shift = 0;                                       // threads a row: the power of two that holds the head (no division an element)
+    while ((1 << shift) < width) ++shift;
+    const int e = threadIdx.x & ((1 << shift) - 1), rows_a_pass = blockDim.x >> shift;
+    if (e < width) {
+        for (int r = threadIdx.x >> shift; r < nrows; r += rows_a_pass) {
+            const int src = first + r;
+            sm[r * width + e] = src >= 0 ? to_f<TA>(proj[(size_t)(t0 + src) * stride + base + e])
+                                         : st[(size_t)(taps - 1 + src) * C + base + e];
+        }
     }
     for (int i = threadIdx.x; i < width * taps; i += blockDim.x) ws[i] = to_f<TW>(taps_w[(size_t)base * taps + i]);
     __syncthreads();
@@ -118,11 +124,11 @@ __global__ void __launch_bounds__(256) conv_prep_tile_kernel(const TA* __restric
         float ss = 0.f;
 #pragma unroll
         for (int m = 0; m < CONV_KEEP; ++m) {
-            const int e = lane + 32 * m;
+            const int el = lane + 32 * m;
             float v = 0.f;
-            if (e < width) {
+            if (el < width) {
                 float acc = 0.f;
-                for (int j = 0; j < taps; ++j) acc = fmaf(ws[e * taps + j], rows[(size_t)j * width + e], acc);
+                for (int j = 0; j < taps; ++j) acc = fmaf(ws[el * taps + j], rows[(size_t)j * width + el], acc);
                 v = acc / (1.0f + expf(-acc));
             }
             y[m] = v;
@@ -132,8 +138,8 @@ __global__ void __launch_bounds__(256) conv_prep_tile_kernel(const TA* __restric
         if (qk) r = (1.0f / sqrtf(warp_sum(ss) + unit_eps)) * unit_scale;
 #pragma unroll
         for (int m = 0; m < CONV_KEEP; ++m) {
-            const int e = lane + 32 * m;
-            if (e < width) out[(size_t)t * C + base + e] = qk ? y[m] * r : y[m];
+            const int el = lane + 32 * m;
+            if (el < width) out[(size_t)t * C + base + el] = qk ? y[m] * r : y[m];
         }
     }
 }
