@@ -226,14 +226,22 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + lo
 // AHEAD: the next chunk's rows wait in registers while a chunk is worked through (requests of more tokens than a chunk); without
 // it the kernel needs 48 registers instead of 120 and more blocks share an SM, which is what a step of single tokens, all
 // loads and stores of state, wants.  The arithmetic is the same.
-template <int R, int IS, bool AHEAD>
+// COMP (the 32-bit engine): every state element is a pair of floats, S + L, where L gathers what the roundings of S lose: the
+// decay and the write are done as error-free steps (the exact error of a product by a fused multiply-add, of a sum by the six
+// additions of the two-sum), and both column sums read S and L.  A float state gathers one rounding a token, and its read-out
+// is a small difference of large sums: after a thousand tokens that is a relative error of 2e-5 in the read-out; the pair
+// keeps it near 1e-6, the level of the sums themselves.  The slot holds S, then L.  The decay is a pair as well, g = gh + gl:
+// a decay just under one loses up to 3e-8 of itself when it is rounded to a float, the same 3e-8 every time the same token
+// comes again, so a far token's weight, a product of a thousand decays, would be off by 3e-5; gl = expm1(x) - (gh - 1) holds
+// what gh = exp(x) lost (x, the small exponent, carries it).
+template <int R, int IS, bool AHEAD, bool COMP>
 __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const DeltaArgs A) {
     using Sh = DeltaShape<R, IS>;
     constexpr int NT = Sh::NT, PB = Sh::PB, RS = Sh::RS, TS = Sh::TS, CH = Sh::CH;
     __shared__ __align__(16) float qs[CH * TS];
     __shared__ __align__(16) float ks[CH * TS];
     __shared__ float vs[CH * DELTA_JS];
-    __shared__ float gg[CH], gb[CH];
+    __shared__ float gg[CH], gb[CH], gl[COMP ? CH : 1];
     const int d = A.d;
     const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
     const int hq = h / (A.H / A.nqk);                            // the q/k head this value head reads
@@ -242,10 +250,14 @@ __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const
     grid_dependency_trigger();
     const int t0 = A.q_start[b], t1 = A.q_start[b + 1];
     if (t0 >= t1) return;
-    float* st = A.state + (size_t)A.slots[b] * A.slot_stride + ((size_t)h * gridDim.z + z) * PB;
-    float S[R];
+    float* st = A.state + (size_t)A.slots[b] * A.slot_stride + ((size_t)h * gridDim.z + z) * (COMP ? 2 * PB : PB);
+    float S[R], L[COMP ? R : 1];
 #pragma unroll
     for (int r = 0; r < R; ++r) S[r] = st[r * NT + tid];
+    if constexpr (COMP) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) L[r] = st[PB + r * NT + tid];
+    }
     const int jcol = z * DELTA_JS + j;
     const bool live = jcol < A.dv;
     const float neg_rate = -expf(A.A_log[h]), bias = A.dt_bias[h];
@@ -317,7 +329,9 @@ __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const
         }
         if (tid < n) {
             gb[tid] = 1.0f / (1.0f + expf(-fgb));
-            gg[tid] = expf(neg_rate * softplus_f(fga + bias));
+            const float x = neg_rate * softplus_f(fga + bias);
+            gg[tid] = expf(x);
+            if constexpr (COMP) gl[tid] = __fsub_rn(expm1f(x), __fsub_rn(gg[tid], 1.0f));
         }
         __syncthreads();
         if (AHEAD && c0 + CH < t1) fetch(c0 + CH);
@@ -327,6 +341,33 @@ __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const
             // S^T k is taken of the state before the decay and multiplied by g once (the same sum); the decay and the
             // write are then one fused multiply-add an element, so a step rounds the state once, not twice
             const float g = gg[t];
+            if constexpr (COMP) {
+                float acc = 0.f, accl = 0.f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) { acc = fmaf(S[r], kt[t * TS + r], acc); accl = fmaf(L[r], kt[t * TS + r], accl); }
+                acc += accl;
+#pragma unroll
+                for (int o = 1; o < IS; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                const float glo = gl[t];
+                const float u = gb[t] * (vs[t * DELTA_JS + j] - fmaf(glo, acc, g * acc));
+                float rd = 0.f, rdl = 0.f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float k = kt[t * TS + r], q = qt[t * TS + r];
+                    const float p = __fmul_rn(k, u), pe = __fmaf_rn(k, u, -p);           // k u = p + pe exactly
+                    const float gs = __fmul_rn(g, S[r]), gse = __fmaf_rn(g, S[r], -gs);   // g S = gs + gse exactly
+                    const float sum = __fadd_rn(gs, p), bb = __fsub_rn(sum, gs);          // gs + p = sum + se exactly
+                    const float se = __fadd_rn(__fsub_rn(gs, __fsub_rn(sum, bb)), __fsub_rn(p, bb));
+                    L[r] = __fmaf_rn(glo, S[r], __fmaf_rn(g, L[r], __fadd_rn(__fadd_rn(se, gse), pe)));
+                    S[r] = sum;
+                    rd = fmaf(S[r], q, rd); rdl = fmaf(L[r], q, rdl);
+                }
+                rd += rdl;
+#pragma unroll
+                for (int o = 1; o < IS; o <<= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
+                if (live && islice == 0) A.out[(size_t)(c0 + t) * A.H * A.dv + (size_t)h * A.dv + jcol] = rd;
+                continue;
+            }
             float acc = 0.f;
 #pragma unroll
             for (int r = 0; r < R; r += 4) {
@@ -357,17 +398,23 @@ __global__ void __launch_bounds__(DeltaShape<R, IS>::NT) delta_scan_kernel(const
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) st[r * NT + tid] = S[r];
+    if constexpr (COMP) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) st[PB + r * NT + tid] = L[r];
+    }
 }
 
 // How a head of d rows is dealt out: 0: R 4 x IS 8 (d <= 32), 1: 8 x 8 (<= 64), 2: 8 x 16 (<= 128), 3: 8 x 32 (<= 256); -1: too large.
 static int delta_shape(int d) { return d <= 32 ? 0 : d <= 64 ? 1 : d <= 128 ? 2 : d <= 256 ? 3 : -1; }
 
-TL_EXPORT int tl_delta_state_floats(int d) {
+// Floats of state per (head, column slice) for a head of d rows (twice as many with the pair of floats an element); 0: too large.
+TL_EXPORT int tl_delta_state_floats(int d, int compensated) {
+    const int f = compensated ? 2 : 1;
     switch (delta_shape(d)) {
-        case 0: return DeltaShape<4, 8>::PB;
-        case 1: return DeltaShape<8, 8>::PB;
-        case 2: return DeltaShape<8, 16>::PB;
-        case 3: return DeltaShape<8, 32>::PB;
+        case 0: return f * DeltaShape<4, 8>::PB;
+        case 1: return f * DeltaShape<8, 8>::PB;
+        case 2: return f * DeltaShape<8, 16>::PB;
+        case 3: return f * DeltaShape<8, 32>::PB;
     }
     return 0;
 }
@@ -375,15 +422,16 @@ TL_EXPORT int tl_delta_columns() { return DELTA_JS; }
 
 TL_EXPORT int tl_delta_scan(const float* qkv, int stride, int q_off, int k_off, int v_off, const float* gates, int gate_stride,
                             const float* A_log, const float* dt_bias, float* state, long long slot_stride, const int* q_start,
-                            const int* slots, float* out, int B, int H, int nqk, int d, int dv, int max_q_len, cudaStream_t stream) {
+                            const int* slots, float* out, int B, int H, int nqk, int d, int dv, int max_q_len, int compensated,
+                            cudaStream_t stream) {
     if (B <= 0 || H <= 0) return 0;
     if (H > 65535 || nqk < 1 || H % nqk) return 1;
     const DeltaArgs A{qkv, stride, q_off, k_off, v_off, gates, gate_stride, A_log, dt_bias, state, slot_stride, q_start, slots, out,
                       H, nqk, d, dv};
     const dim3 grid(B, H, (dv + DELTA_JS - 1) / DELTA_JS);
-#define DS(R_, IS_) (max_q_len > DeltaShape<R_, IS_>::CH \
-        ? launch_after_wait(delta_scan_kernel<R_, IS_, true>, grid, dim3(DeltaShape<R_, IS_>::NT), 0, stream, A) \
-        : launch_after_wait(delta_scan_kernel<R_, IS_, false>, grid, dim3(DeltaShape<R_, IS_>::NT), 0, stream, A))
+#define DSK(R_, IS_, AH, CO) launch_after_wait(delta_scan_kernel<R_, IS_, AH, CO>, grid, dim3(DeltaShape<R_, IS_>::NT), 0, stream, A)
+#define DS(R_, IS_) (compensated ? (max_q_len > DeltaShape<R_, IS_>::CH ? DSK(R_, IS_, true, true) : DSK(R_, IS_, false, true)) \
+                                 : (max_q_len > DeltaShape<R_, IS_>::CH ? DSK(R_, IS_, true, false) : DSK(R_, IS_, false, false)))
     switch (delta_shape(d)) {
         case 0: return DS(4, 8);
         case 1: return DS(8, 8);
@@ -391,5 +439,6 @@ TL_EXPORT int tl_delta_scan(const float* qkv, int stride, int q_off, int k_off, 
         case 3: return DS(8, 32);
     }
 #undef DS
+#undef DSK
     return 1;
 }

@@ -44,8 +44,8 @@ _SIGNATURES = {
     "tl_relu_square": [_P, _I, ctypes.c_longlong, _P],
     "tl_moe_combine": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _P],
     "tl_conv_prep": [_P, _I, _I, _P, _I, _I, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
-    "tl_delta_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "tl_delta_state_floats": [_I],
+    "tl_delta_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "tl_delta_state_floats": [_I, _I],
     "tl_delta_columns": [],
     "tl_latent_prep": [_P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "tl_latent_qrot": [_P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -683,9 +683,10 @@ def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, idx: torch.Tensor, o
 # ---------------------------------------------------------------------------------------------
 # The gated delta rule (csrc/delta.cu)
 
-def delta_state_floats(d: int) -> int:
-    """Floats of state that `delta_scan` keeps per (head, slice of `delta_columns()` value columns) for heads of d rows."""
-    n = core().tl_delta_state_floats(int(d))
+def delta_state_floats(d: int, compensated: bool = False) -> int:
+    """Floats of state that `delta_scan` keeps per (head, slice of `delta_columns()` value columns) for heads of d rows; twice
+    as many when every element is a pair of floats (`compensated`)."""
+    n = core().tl_delta_state_floats(int(d), int(compensated))
     if n <= 0:
         raise KernelError(f"delta_scan: heads of {d} rows are not supported (at most 256)")
     return n
@@ -722,12 +723,14 @@ def conv_prep(proj: torch.Tensor, taps_w: torch.Tensor, conv_state: torch.Tensor
 
 def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
                q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, *, B: int, H: int, nqk: int, d: int, dv: int,
-               max_q_len: int | None = None) -> None:
+               max_q_len: int | None = None, compensated: bool = False) -> None:
     """Per (request, head), tokens in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
     beta = sigmoid(gates[t, h]) and g = exp(-exp(A_log[h]) softplus(gates[t, H + h] + dt_bias[h])).  qkv float32 [T, C] as
     `conv_prep` leaves it (q [nqk, d], k [nqk, d], v [H, dv]; head h reads q/k head h // (H / nqk)); the state is read from
     and left in `state[slot]` (float32, `delta_state_floats` per head and column slice); out float32 [T, H dv].  `max_q_len`: the most tokens a request brings
-    (None: as many as the step has); it only picks between two forms of the kernel that give the same bits."""
+    (None: as many as the step has); it only picks between two forms of the kernel that give the same bits.  `compensated`:
+    every state element is a pair of floats whose second gathers what the roundings of the first lose (the decay and the write as
+    error-free steps): the state then stays at the accuracy of the sums that feed it however many tokens it has seen."""
     T = qkv.shape[0]
     C = 2 * nqk * d + H * dv
     if qkv.dtype != torch.float32 or qkv.shape != (T, C) or out.dtype != torch.float32 or out.shape != (T, H * dv):
@@ -738,12 +741,12 @@ def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, A_log: torch.Tensor, dt_b
         if t.dtype != torch.float32 or t.numel() != H or not t.is_contiguous():
             raise KernelError(f"delta_scan: {name} must be float32 [H]")
     _contig(qkv, "qkv"); _contig(out, "out"); _contig(state, "state"); _ints(q_start, "q_start"); _ints(slots, "slots")
-    per_slot = H * -(-dv // delta_columns()) * delta_state_floats(d)
+    per_slot = H * -(-dv // delta_columns()) * delta_state_floats(d, compensated)
     if state.dtype != torch.float32 or state[0].numel() != per_slot:
         raise KernelError(f"delta_scan: a slot holds {state[0].numel()} floats, these sizes need {per_slot}")
     _check(core().tl_delta_scan(_ptr(qkv), C, 0, nqk * d, 2 * nqk * d, _ptr(gates), gates.stride(0), _ptr(A_log), _ptr(dt_bias),
                                 _ptr(state), per_slot, _ptr(q_start), _ptr(slots), _ptr(out), int(B), H, nqk, d, dv,
-                                int(T if max_q_len is None else max_q_len), _stream()),
+                                int(T if max_q_len is None else max_q_len), int(compensated), _stream()),
            "delta_scan")
 
 

@@ -39,6 +39,9 @@ class GatedDelta(Part):
             raise ValueError(f"head_dim {head_dim}: the scan kernel keeps at most 256 rows of state a head")
         self.hidden, self.H, self.nqk, self.d, self.dv, self.taps, self.eps = hidden, num_heads, num_qk_heads, head_dim, v_head_dim, taps, norm_eps
         self.C = 2 * num_qk_heads * head_dim + num_heads * v_head_dim          # channels that pass the convolution
+        # the 32-bit engine keeps every state element as a pair of floats (see csrc/delta.cu): a float alone gathers one
+        # rounding a token, which a read-out that is a small difference of large sums shows after a thousand tokens
+        self.compensated = rt.exact
         self.names = {**_NAMES, **(names or {})}
         self.w_in = self.w_o = self.taps_w = self.A_log = self.dt_bias = self.head_weight = None
 
@@ -46,7 +49,7 @@ class GatedDelta(Part):
         """As `ops.delta_state_floats` says on the device: R rows in each of IS x 16 threads."""
         d = self.d
         rows, per_column = (4, 8) if d <= 32 else (8, 8) if d <= 64 else (8, 16) if d <= 128 else (8, 32)
-        return rows * per_column * 16
+        return rows * per_column * 16 * (2 if self.compensated else 1)
 
     def cache_need(self):
         need = {"memory": SlotState((self.H * -(-self.dv // 16) * self._state_floats(),), "float32")}
@@ -73,7 +76,7 @@ class GatedDelta(Part):
         self.head_weight = weights[n["norm"]].repeat(self.H).contiguous()      # one weight for all heads
         self.w_o = self._compute_copy(weights[n["o"]])
         if self.rt.device.type == "cuda":
-            if ops.delta_columns() != 16 or ops.delta_state_floats(self.d) != self._state_floats():
+            if ops.delta_columns() != 16 or ops.delta_state_floats(self.d, self.compensated) != self._state_floats():
                 raise ops.KernelError("the delta kernel's state layout is not the one this mixer sizes its slots for")
 
     def forward(self, h, ctx, cache):
@@ -88,7 +91,7 @@ class GatedDelta(Part):
                       nv=H, dv=dv, unit_eps=self.unit_eps, q_scale=d ** -0.5)
         o = torch.empty((T, H * dv), dtype=torch.float32, device=h.device)
         ops.delta_scan(qkv, gates, self.A_log, self.dt_bias, cache["memory"].state, ctx.q_start, ctx.slots, o, B=ctx.B, H=H,
-                       nqk=nqk, d=d, dv=dv, max_q_len=ctx.max_q_len)
+                       nqk=nqk, d=d, dv=dv, max_q_len=ctx.max_q_len, compensated=self.compensated)
         y = torch.empty((T, H * dv), dtype=h.dtype, device=h.device)
         ops.head_norm_gate(o, y, H, dv, self.eps, weight=self.head_weight, gate=proj, gate_off=C, act="silu")
         return matmul(y, self.w_o)

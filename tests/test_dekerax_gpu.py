@@ -193,10 +193,12 @@ def _gates_plain(gates, A_log, dt_bias, H):
     return beta, g
 
 
+@pytest.mark.parametrize("pair", [False, True], ids=["float", "pair"])
 @pytest.mark.parametrize("H,nqk,d,dv", [(4, 2, 8, 24), (1, 1, 40, 72), (2, 2, 136, 8), (6, 2, 20, 12), (3, 1, 256, 16), (2, 2, 64, 33)])
-def test_delta_rule_in_one_step_and_in_portions(H, nqk, d, dv):
+def test_delta_rule_in_one_step_and_in_portions(H, nqk, d, dv, pair):
     """The recurrence over whole requests in one launch against the formula, and the same requests cut into portions
-    (single tokens among them) over several launches with the state left in the slots: the same bits."""
+    (single tokens among them) over several launches with the state left in the slots: the same bits.  `pair`: the state as
+    the 32-bit engine keeps it, two floats an element."""
     from tensorline_b200 import ops
     lens = [37, 1, 5, 70]
     T, C = sum(lens), 2 * nqk * d + H * dv
@@ -208,7 +210,8 @@ def test_delta_rule_in_one_step_and_in_portions(H, nqk, d, dv):
     beta, g = _gates_plain(gates, A_log, dt_bias, H)
     want = _delta_plain(qkv[:, :nqk * d].double().view(T, nqk, d), qkv[:, nqk * d:2 * nqk * d].double().view(T, nqk, d),
                         qkv[:, 2 * nqk * d:].double().view(T, H, dv), beta, g, lens).reshape(T, H * dv)
-    per_slot = H * -(-dv // ops.delta_columns()) * ops.delta_state_floats(d)
+    per_slot = H * -(-dv // ops.delta_columns()) * ops.delta_state_floats(d, pair)
+    assert ops.delta_state_floats(d, True) == 2 * ops.delta_state_floats(d, False)
     slots = [5, 0, 3, 2]
 
     def run(cuts):
@@ -220,7 +223,7 @@ def test_delta_rule_in_one_step_and_in_portions(H, nqk, d, dv):
             idx = torch.tensor(rows)
             part = torch.zeros(len(rows), H * dv, device="cuda")
             ops.delta_scan(qkv[idx].contiguous().cuda(), gates[idx].contiguous().cuda(), A_log.cuda(), dt_bias.cuda(), state,
-                           i32(q_start), i32(live), part, B=len(live), H=H, nqk=nqk, d=d, dv=dv)
+                           i32(q_start), i32(live), part, B=len(live), H=H, nqk=nqk, d=d, dv=dv, compensated=pair)
             out[idx.cuda()] = part
         _run_in_cuts(lens, cuts, slots, step)
         assert bool((state[1] == 7.0).all()) and bool((state[[4, 6]] == 0).all())
@@ -230,6 +233,35 @@ def test_delta_rule_in_one_step_and_in_portions(H, nqk, d, dv):
     assert_close(whole, want, "delta rule", rtol=5e-5, atol=5e-5)
     assert torch.equal(run(CUTS[1:]), whole)
     assert torch.equal(run(CUTS_SINGLE), whole)
+
+
+def test_a_pair_of_floats_keeps_the_state_exact_over_many_tokens():
+    """1,500 tokens, most of them one of three that come again and again, with decays just under one.  A decay rounded to a float
+    is off by the same 3e-8 whenever its token comes again, so the weight of a far token, a product of a thousand decays, drifts
+    from the float64 recurrence by 1e-5 and more, and a float state gathers a rounding a token on top; with pairs of floats for
+    the state and the decay (the 32-bit engine) the read-out stays at the accuracy of the sums that feed it."""
+    from tensorline_b200 import ops
+    H, nqk, d, dv, T = 2, 1, 32, 48, 1500
+    kinds = rnd(3, 2 * nqk * d + H * dv, seed=7)
+    which = torch.randint(0, 3, (T,), generator=torch.Generator().manual_seed(9))
+    qkv = kinds[which].clone()
+    qkv[::50] = rnd(T // 50, qkv.shape[1], seed=10)              # now and then another token
+    qk = qkv[:, :2 * nqk * d].view(T, 2 * nqk, d)
+    qkv[:, :2 * nqk * d] = (qk / qk.norm(dim=-1, keepdim=True)).reshape(T, -1)
+    gates = rnd(3, 2 * H, seed=8)[which].contiguous()
+    A_log, dt_bias = torch.tensor([-7.0, -6.0]), torch.zeros(H)
+    beta, g = _gates_plain(gates, A_log, dt_bias, H)
+    want = _delta_plain(qkv[:, :d].double().view(T, 1, d), qkv[:, d:2 * d].double().view(T, 1, d), qkv[:, 2 * d:].double().view(T, H, dv),
+                        beta, g, [T])
+    errs = {}
+    for pair in (False, True):
+        state = torch.zeros(2, H * -(-dv // ops.delta_columns()) * ops.delta_state_floats(d, pair), device="cuda")
+        out = torch.zeros(T, H * dv, device="cuda")
+        ops.delta_scan(qkv.cuda(), gates.cuda(), A_log.cuda(), dt_bias.cuda(), state, i32([0, T]), i32([1]), out, B=1, H=H, nqk=nqk,
+                       d=d, dv=dv, compensated=pair)
+        e = (out.double().cpu().view(T, H, dv) - want)[-200:]
+        errs[pair] = float(e.pow(2).sum().sqrt() / want[-200:].pow(2).sum().sqrt())
+    assert errs[True] < 3e-6 and errs[True] < 0.25 * errs[False], errs
 
 
 @pytest.mark.parametrize("decoded", [0, 300])
